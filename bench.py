@@ -1,0 +1,358 @@
+"""Benchmark of the triangle-attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg3] [--impl ours|reference]
+
+One "step" is one forward + backward call of starting-node triangle attention on
+synthetic inputs of the named BASELINE configuration (bf16, H=4, D=32, shared
+bias, all-ones mask).  With N > 1 (launched by torchrun, one rank per GPU) the
+pair rows are sharded across ranks; each step then also all-gathers the bias
+shards and reduce-scatters the bias gradient (strong scaling: the total work is
+fixed).  Rank 0 prints one JSON line.
+
+`--impl reference` times the reference's own CPU math (the oracle restatement of
+its PyTorch `_reference`) on the host cores, on a bounded sample of rows of the
+same configuration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (N, heads, head_dim) -- BASELINE configs 5 and 3
+    "cfg5": dict(n=2048, heads=4, dim=32, label="config 5: starting node, bf16, fwd+bwd, B=1, N=2048, H=4, D=32"),
+    "cfg3": dict(n=768, heads=4, dim=32, label="config 3: starting node, bf16, fwd+bwd, B=1, N=768, H=4, D=32"),
+}
+FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def flops(rows: int, cols: int, heads: int, dim: int, backward: bool) -> float:
+    return float(rows) * heads * cols * cols * dim * (14.0 if backward else 4.0)
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            return float(data["bf16_tflops"]), float(data.get("bf16_tflops_sustained", data["bf16_tflops"])), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return FALLBACK_PEAK_TFLOPS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self._nvml = None
+
+    def _run(self):
+        nvml = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM))
+                bits = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def make_inputs(n, heads, dim, row_lo, row_hi, seed):
+    """Synthetic inputs of the configuration for rows [row_lo, row_hi): N(0,1)*0.5 q/k/v, N(0,1) bias and upstream."""
+    gen = torch.Generator().manual_seed(seed)
+    rows = row_hi - row_lo
+    q, k, v = ((torch.randn(1, rows, n, heads, dim, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(3))
+    upstream = torch.randn(1, rows, n, heads, dim, generator=gen).to(torch.bfloat16)
+    bias_shard = torch.randn(1, 1, heads, rows, n, generator=gen).to(torch.bfloat16)  # query rows [row_lo, row_hi)
+    mask = torch.ones(1, rows, n, dtype=torch.bool)
+    return q, k, v, upstream, bias_shard, mask
+
+
+def cpu_oracle_rate(n, heads, dim, budget_s, threads):
+    """Time the oracle's forward+backward on a bounded sample of rows; returns (TFLOP/s, rows, seconds)."""
+    from oracle import triangle_oracle as oracle
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(1)
+    bias = torch.randn(1, 1, heads, n, n, generator=gen)
+
+    def run(rows):
+        q, k, v, up = (torch.randn(1, rows, n, heads, dim, generator=gen) * 0.5 for _ in range(4))
+        mask = torch.ones(1, rows, n, dtype=torch.bool)
+        t0 = time.perf_counter()
+        oracle.forward_backward(q, k, v, mask, bias, up, budget_bytes=1 << 30)
+        return time.perf_counter() - t0
+
+    run(1)  # warm-up
+    probe = run(2)
+    rows = int(max(2, min(n, budget_s / max(probe / 2, 1e-6))))
+    seconds = run(rows)
+    return flops(rows, n, heads, dim, True) / seconds / 1e12, rows, seconds
+
+
+def reference_arm(args, work):
+    """The reference's CPU math on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n, heads, dim = work["n"], work["heads"], work["dim"]
+    threads = os.cpu_count() or 1
+    budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_oracle_rate(n, heads, dim, budget / 4, threads)
+    rates, rows_used, secs = [], 0, []
+    for _ in range(args.steps):
+        rate, rows_used, seconds = cpu_oracle_rate(n, heads, dim, budget, threads)
+        rates.append(rate)
+        secs.append(seconds)
+    value = statistics.mean(rates)
+    sample = f"{rows_used} of {n} rows per step (rows are independent), f32, all host threads"
+    line = {
+        "impl": "reference", "metric": "triangle_attention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * statistics.mean(secs), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": work["label"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg5")
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-extra", action="store_true", help="skip the secondary N=768 measurement")
+    args = parser.parse_args()
+    work = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, work)
+        return
+
+    import torch.distributed as dist
+
+    from oops_b200 import triangle_attention
+    from oops_b200.distributed.row_shard import row_sharded_triangle_attention, shard_bounds
+    from oops_b200.runtime import cabi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run); got {world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (there is no CPU fallback)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+    cabi.library()
+
+    n, heads, dim = work["n"], work["heads"], work["dim"]
+    lo, hi = shard_bounds(n, world, rank)
+    host = [t.pin_memory() for t in make_inputs(n, heads, dim, lo, hi, seed=100 + rank)]
+    q, k, v, upstream, bias_shard, mask = (t.to(device) for t in host)
+    q, k, v, bias_shard = (t.requires_grad_(True) for t in (q, k, v, bias_shard))
+
+    def step(q, k, v, bias_shard, mask, upstream):
+        if distributed:
+            out = row_sharded_triangle_attention(q, k, v, mask, bias_shard)
+        else:
+            out = triangle_attention(q, k, v, mask, bias_shard)
+        return torch.autograd.grad(out, (q, k, v, bias_shard), upstream)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters):
+        """Milliseconds per iteration, CUDA events on the current stream, max over ranks."""
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            fn()
+        stop.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(stop) / iters], device=device)
+        if distributed:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident throughput --------------------------------------------------------
+    for _ in range(args.warmup):
+        step(q, k, v, bias_shard, mask, upstream)
+    launches_before = cabi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ms_step = timed(lambda: step(q, k, v, bias_shard, mask, upstream), args.steps)
+    launches = torch.tensor([cabi.launch_count() - launches_before], device=device, dtype=torch.int64)
+    if distributed:
+        dist.all_reduce(launches)
+    total_flops = flops(n, n, heads, dim, True)
+    value = total_flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host inputs in, gradient of the bias out, every step -------------
+    host_out = torch.empty(bias_shard.shape, dtype=torch.bfloat16).pin_memory()
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host)
+    d2h_bytes = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        dq, dk, dv, up, bs, m = (t.to(device, non_blocking=True) for t in host)
+        dq, dk, dv, bs = (t.requires_grad_(True) for t in (dq, dk, dv, bs))
+        grads = step(dq, dk, dv, bs, m, up)
+        host_out.copy_(grads[3], non_blocking=True)
+
+    e2e_iters = max(2, min(args.steps, 5))
+    e2e_step()
+    ms_e2e = timed(e2e_step, e2e_iters)
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+
+    # ---- dominant kernel: the forward kernel, one launch per call, timed alone ---------------
+    peak, peak_sustained, peak_kind = measured_peak()
+    with torch.no_grad():
+        bias_full = None
+        if distributed:
+            from oops_b200.distributed.row_shard import gather_bias
+
+            bias_full = gather_bias(bias_shard.detach())
+        else:
+            bias_full = bias_shard.detach()
+        fwd = lambda: triangle_attention(q.detach(), k.detach(), v.detach(), mask, bias_full)  # noqa: E731
+        for _ in range(3):
+            fwd()
+        before = cabi.launch_count()
+        ms_fwd = timed(fwd, args.steps)
+        fwd_launches = (cabi.launch_count() - before) // args.steps
+    fwd_flops_rank = flops(hi - lo, n, heads, dim, False)
+    fwd_tflops = fwd_flops_rank / (ms_fwd * 1e-3) / 1e12
+    profile = {}
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        try:
+            profile = json.loads(traffic_file.read_text())
+        except Exception:  # noqa: BLE001
+            profile = {}
+    bytes_per_row = profile.get("forward_dram_bytes_per_row_n%d" % n)
+    roofline = {
+        "bound": "tensor", "kernel": "forward (one call; %d launch(es))" % fwd_launches,
+        "achieved": fwd_tflops, "peak": peak, "unit": "TFLOP/s", "frac": fwd_tflops / peak,
+        "peak_kind": peak_kind, "ms": ms_fwd,
+        "traffic": None if bytes_per_row is None else bytes_per_row * (hi - lo),
+    }
+
+    line = {
+        "metric": "triangle_attention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": work["label"], "rows_per_gpu": hi - lo, "sharding": "pair rows; bias all-gather, dbias reduce-scatter"
+            if distributed else "single GPU", "l2": "inputs larger than L2 (no flush needed)",
+            "tensor_path": {"forward": None, "backward": None},
+        },
+        "frac_of_bf16_peak": value / (peak * world), "frac_of_bf16_sustained": value / (peak_sustained * world),
+        "fwd": {"ms": ms_fwd, "tflops_per_gpu": fwd_tflops, "frac_of_bf16_peak": fwd_tflops / peak},
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d_bytes * world,
+                "d2h_bytes_per_step": d2h_bytes * world},
+        "gpu_launches": int(launches.item()),
+        "roofline": roofline,
+    }
+    probe = cabi.make_problem(q.detach(), k.detach(), v.detach(), mask, bias_full, dim**-0.5)
+    line["config"]["tensor_path"] = {
+        "forward": bool(cabi.library().oops_ta_uses_tensor_path(cabi.byref(probe), 0) == 1),
+        "backward": bool(cabi.library().oops_ta_uses_tensor_path(cabi.byref(probe), 1) == 1),
+    }
+
+    # ---- secondary: BASELINE config 3 (N=768) on one GPU -------------------------------------
+    if rank == 0 and not distributed and not args.no_extra and args.workload != "cfg3":
+        n3 = WORKLOADS["cfg3"]["n"]
+        del host
+        t3 = [t.to(device) for t in make_inputs(n3, heads, dim, 0, n3, seed=7)]
+        q3, k3, v3, up3, b3, m3 = t3
+        q3, k3, v3, b3 = (t.requires_grad_(True) for t in (q3, k3, v3, b3))
+        for _ in range(3):
+            step(q3, k3, v3, b3, m3, up3)
+        ms3 = timed(lambda: step(q3, k3, v3, b3, m3, up3), max(args.steps, 10))
+        with torch.no_grad():
+            ms3f = timed(lambda: triangle_attention(q3, k3, v3, m3, b3), max(args.steps, 10))
+        f3, f3f = flops(n3, n3, heads, dim, True), flops(n3, n3, heads, dim, False)
+        line["n768"] = {
+            "workload": WORKLOADS["cfg3"]["label"], "fwd_bwd_ms": ms3, "fwd_bwd_tflops": f3 / ms3 / 1e9,
+            "fwd_bwd_frac_of_bf16_peak": f3 / ms3 / 1e9 / peak, "fwd_ms": ms3f, "fwd_tflops": f3f / ms3f / 1e9,
+            "fwd_frac_of_bf16_peak": f3f / ms3f / 1e9 / peak,
+        }
+
+    # ---- CPU baseline: the oracle on the host cores, bounded sample, rank 0 at N=1 only ------
+    if rank == 0 and not distributed and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        rate, rows_used, seconds = cpu_oracle_rate(n, heads, dim, 12.0, threads)
+        line["cpu_baseline"] = {
+            "value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{rows_used} of {n} rows (rows are independent), f32, {seconds:.1f} s",
+        }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,168 @@
+/*
+ * oops_ta.h -- C ABI of the B200 (sm_100a) triangle-attention library.
+ *
+ * The library replaces the backend of OOps' `oops.attention.triangle_attention`
+ * operator.  In the reference that backend is a set of Triton kernels reached
+ * through Python; it has no C interface of its own, so every entry point below
+ * names the Python function whose work it takes over (paths are relative to the
+ * reference checkout).
+ *
+ * Conventions
+ *   - Plain C: raw device pointers, 64-bit element strides, no framework types.
+ *   - The library never allocates, frees or retains device memory.  The caller
+ *     owns every buffer, including the scratch workspace, whose size it asks
+ *     for with oops_ta_*_workspace_bytes().
+ *   - All work is enqueued on the CUDA stream passed in (a cudaStream_t cast to
+ *     void*); no call synchronises the device.  The current device must be the
+ *     one that owns the buffers.
+ *   - Every function returns an oops_ta_status; 0 is success.  Unsupported
+ *     requests are reported, never served by a fallback.
+ *
+ * Tensor model
+ *   A "pair tensor" (query, key, value, output and their gradients) is addressed
+ *   as  ptr[b*sb + r*sr + c*sc + h*sh + d]  for b<batch, r<rows, c<cols,
+ *   h<heads, d<head_dim: the head_dim axis is contiguous, every other axis has a
+ *   free element stride.  The starting-node form has sr > sc; the ending-node
+ *   form of the reference (pair axes swapped in memory,
+ *   oops/attention/triangle/triangle_attention.py:249-258) is the same call
+ *   with sr < sc.  Ragged (NestedTensor) batches are one call per sample with
+ *   the sample's base pointer and strides (the eight columns of the reference's
+ *   sample table, oops/attention/triangle/nested.py:275-288, become these
+ *   fields).
+ */
+#ifndef OOPS_TA_H_
+#define OOPS_TA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OOPS_TA_ABI_VERSION 1
+
+typedef enum oops_ta_dtype {
+  OOPS_TA_F32 = 0,
+  OOPS_TA_F16 = 1,
+  OOPS_TA_BF16 = 2
+} oops_ta_dtype;
+
+typedef enum oops_ta_status {
+  OOPS_TA_OK = 0,
+  OOPS_TA_INVALID_ARGUMENT = 1,   /* null pointer, bad size, wrong ABI version      */
+  OOPS_TA_UNSUPPORTED_DTYPE = 2,  /* dtype outside {f32, f16, bf16}                  */
+  OOPS_TA_UNSUPPORTED_HEAD_DIM = 3, /* head_dim outside [1, 256]                     */
+  OOPS_TA_UNSUPPORTED_LAYOUT = 4, /* a stride or alignment the kernels cannot take   */
+  OOPS_TA_LIMIT_EXCEEDED = 5,     /* grid or index range beyond 2^31-1               */
+  OOPS_TA_WORKSPACE_TOO_SMALL = 6,
+  OOPS_TA_CUDA_ERROR = 7,         /* a CUDA runtime/driver call failed               */
+  OOPS_TA_DEVICE_TIMEOUT = 8,     /* a bounded device-side wait gave up              */
+  OOPS_TA_WRONG_DEVICE = 9        /* the device is not compute capability 10.x       */
+} oops_ta_status;
+
+/* flags of oops_ta_problem.flags */
+#define OOPS_TA_FLAG_FORCE_GENERIC 1u /* take the layout-agnostic FFMA kernels even
+                                         where the tcgen05 kernels apply (testing) */
+#define OOPS_TA_FLAG_ALLOW_TF32 2u    /* f32 inputs may use TF32-class products; the
+                                         default keeps full f32 products, which is what
+                                         the reference's "ieee"/3xTF32 mode promises
+                                         (oops/runtime/dispatch.py:260-328)           */
+
+typedef struct oops_ta_pair {
+  void* ptr;
+  int64_t sb, sr, sc, sh; /* element strides of batch, row, column, head */
+} oops_ta_pair;
+
+/*
+ * One uniform problem: `batch` independent pair tensors of rows x cols cells.
+ * Replaces the argument bundle the reference hands to its Triton launchers
+ * (oops/attention/triangle/triton/generic.py:173-317 forward, :320-534 reverse).
+ */
+typedef struct oops_ta_problem {
+  uint32_t abi_version; /* OOPS_TA_ABI_VERSION */
+  uint32_t flags;
+  int32_t dtype;       /* oops_ta_dtype of q, k, v, out and their gradients         */
+  int32_t bias_dtype;  /* oops_ta_dtype of bias and its gradient (dtype or F32)     */
+  int32_t batch, rows, cols, heads, head_dim;
+  int32_t bias_groups; /* 0: no bias; 1: one bias shared by all rows; rows: per row  */
+  float scale;         /* multiplies q.k before the bias is added                   */
+  int32_t reserved;
+
+  oops_ta_pair q, k, v;
+
+  /* keep-mask over keys: nonzero byte keeps key column c of row r.  NULL keeps all.
+     Strides may be 0 (broadcast).  Replaces the int16 mask of
+     oops/attention/triangle/triangle_attention.py:135. */
+  const uint8_t* mask;
+  int64_t mask_sb, mask_sr, mask_sc;
+
+  /* bias[b*sb + g*sg + h*sh + q*sq + k*sk], g = 0 when bias_groups == 1 else r. */
+  const void* bias;
+  int64_t bias_sb, bias_sg, bias_sh, bias_sq, bias_sk;
+
+  void* workspace;
+  uint64_t workspace_bytes;
+} oops_ta_problem;
+
+/* Gradient request of the reverse pass; a NULL ptr skips that gradient
+   (the reference's need_grad_{query,key,value,bias}, generic.py:320-343). */
+typedef struct oops_ta_grads {
+  oops_ta_pair dq, dk, dv;
+  void* dbias; /* same dtype as bias; row-shared biases receive the sum over rows */
+  int64_t dbias_sb, dbias_sg, dbias_sh, dbias_sq, dbias_sk;
+} oops_ta_grads;
+
+/* ABI version the library was built with. */
+int oops_ta_abi_version(void);
+
+/* Static text for a status code. */
+const char* oops_ta_status_string(int status);
+
+/* Detail of the last failure on the calling thread (empty string if none). */
+const char* oops_ta_last_error(void);
+
+/*
+ * Admission test: OOPS_TA_OK if oops_ta_forward/backward can serve the problem,
+ * otherwise the status they would return.  Pointers are not dereferenced.
+ * Replaces supports_triangle_attention (generic.py:64-154).
+ */
+int oops_ta_supported(const oops_ta_problem* problem);
+
+/* 1 if the problem takes the tcgen05/TMEM/TMA kernels, 0 if it takes the
+   layout-agnostic kernels, negative status on error.  `backward` selects which
+   pass is asked about. */
+int oops_ta_uses_tensor_path(const oops_ta_problem* problem, int backward);
+
+/* Scratch bytes oops_ta_forward needs for this problem (may be 0). */
+uint64_t oops_ta_forward_workspace_bytes(const oops_ta_problem* problem);
+
+/* Scratch bytes oops_ta_backward needs for this problem and gradient request. */
+uint64_t oops_ta_backward_workspace_bytes(const oops_ta_problem* problem, const oops_ta_grads* grads);
+
+/*
+ * Forward pass.  Writes out (same dtype as q) and, when lse is not NULL, the
+ * natural-log row normaliser lse[((b*rows + r)*heads + h)*cols + q] (0 for rows
+ * with no kept key, whose output is 0 too).
+ * Replaces _run_forward / _run_inference and the Triton kernels `_forward` /
+ * `_inference` (generic.py:173-317; triton/kernel.py:150-371).
+ */
+int oops_ta_forward(const oops_ta_problem* problem, const oops_ta_pair* out, float* lse, void* stream);
+
+/*
+ * Reverse pass for the gradients requested in `grads`, from the forward output,
+ * its lse and the upstream gradient `dout` (dtype of q).
+ * Replaces _run_backward and the Triton kernels `_backward_preprocess`,
+ * `_backward_query`, `_backward_key_value`, `_backward_shared_bias`
+ * (generic.py:320-534; triton/kernel.py:374-873).
+ */
+int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, const oops_ta_pair* dout,
+                     const float* lse, const oops_ta_grads* grads, void* stream);
+
+/* Number of kernels the library has launched in this process (all streams). */
+uint64_t oops_ta_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OOPS_TA_H_ */

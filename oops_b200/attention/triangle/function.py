@@ -1,0 +1,282 @@
+"""Autograd boundary of triangle attention over the C ABI.
+
+Takes the place of ``oops/attention/triangle/triton/ops.py`` in the reference
+(``_TriangleAttention`` :413, ``_setup_context`` :369, ``_backward_from_context``
+:380): gradients for query, key, value and bias only; mask and the saved
+log-sum-exp are not differentiable; undefined upstream gradients are not
+materialised; the reverse pass honours ``needs_input_grad`` subsets; no double
+backward.
+
+A call is described by a *geometry*: a recipe that turns the tensors handed to
+the Function into one or more uniform ``(B, R, C, H, D)`` views, each of which is
+one C-ABI problem.  Dense inputs are a single view (the tensor itself, whatever
+its strides).  A packed ragged batch is one view per sample, computed from the
+packed layout the reference documents in ``oops/attention/triangle/nested.py:
+275-288`` (cell start, cell stride = number of prefixes, bias start/strides).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+from ...runtime import cabi
+
+
+@dataclass(frozen=True)
+class DenseGeometry:
+    """One uniform problem: the tensors are already ``(B, R, C, H, D)`` views."""
+
+    def pair_views(self, tensor: Tensor) -> List[Tensor]:
+        return [tensor]
+
+    def mask_views(self, mask: Tensor) -> List[Tensor]:
+        return [mask]
+
+    def bias_views(self, bias: Tensor) -> List[Tensor]:
+        return [bias]
+
+    def lse_sizes(self, query: Tensor) -> List[Tuple[int, int, int, int]]:
+        batch, rows, cols, heads, _ = query.shape
+        return [(batch, rows, heads, cols)]
+
+    def canonical_pair(self, tensor: Tensor) -> Tensor:
+        return tensor if tensor.shape[-1] == 1 or tensor.stride(-1) == 1 else tensor.contiguous()
+
+    def canonical_bias(self, bias: Tensor) -> Tensor:
+        return bias
+
+
+@dataclass(frozen=True)
+class NestedGeometry:
+    """Packed ragged batch of square samples.
+
+    Pair tensors are ``(cells, P, H, D)`` contiguous, masks ``(cells, P)``, and the
+    bias is head-major ``(P, H, bias_values)`` with each sample's block laid out as
+    ``(groups, query, key)``.  ``transposed`` means that the packed cell order is
+    column-major (the ending-node form).
+    """
+
+    lengths: Tuple[int, ...]
+    prefixes: int
+    transposed: bool
+    bias_groups: Tuple[int, ...] = ()
+
+    def _cell_starts(self) -> List[int]:
+        starts, at = [], 0
+        for n in self.lengths:
+            starts.append(at)
+            at += n * n
+        return starts
+
+    def pair_views(self, tensor: Tensor) -> List[Tensor]:
+        _, prefixes, heads, dim = tensor.shape
+        cell = prefixes * heads * dim
+        views = []
+        for n, start in zip(self.lengths, self._cell_starts()):
+            major, minor = n * cell, cell
+            row_stride, col_stride = (minor, major) if self.transposed else (major, minor)
+            views.append(
+                tensor.as_strided(
+                    (prefixes, n, n, heads, dim),
+                    (heads * dim, row_stride, col_stride, dim, 1),
+                    tensor.storage_offset() + start * cell,
+                )
+            )
+        return views
+
+    def mask_views(self, mask: Tensor) -> List[Tensor]:
+        prefixes = mask.shape[1]
+        views = []
+        for n, start in zip(self.lengths, self._cell_starts()):
+            major, minor = n * prefixes, prefixes
+            row_stride, col_stride = (minor, major) if self.transposed else (major, minor)
+            views.append(
+                mask.as_strided((prefixes, n, n), (1, row_stride, col_stride), mask.storage_offset() + start * prefixes)
+            )
+        return views
+
+    def bias_views(self, bias: Tensor) -> List[Tensor]:
+        prefixes, heads, total = bias.shape
+        views, at = [], 0
+        for n, groups in zip(self.lengths, self.bias_groups):
+            views.append(
+                bias.as_strided(
+                    (prefixes, groups, heads, n, n), (heads * total, n * n, total, n, 1), bias.storage_offset() + at
+                )
+            )
+            at += groups * n * n
+        return views
+
+    def lse_sizes(self, query: Tensor) -> List[Tuple[int, int, int, int]]:
+        heads = query.shape[2]
+        return [(self.prefixes, n, heads, n) for n in self.lengths]
+
+    def canonical_pair(self, tensor: Tensor) -> Tensor:
+        return tensor.contiguous()
+
+    def canonical_bias(self, bias: Tensor) -> Tensor:
+        return bias.contiguous()
+
+
+def _current_stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _workspace(nbytes: int, device: torch.device) -> Optional[Tensor]:
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device) if nbytes else None
+
+
+def _raise_status(status: int, what: str) -> None:
+    message = f"triangle_attention {what} failed: {cabi.status_message(status)}"
+    if status in (cabi.STATUS_INVALID_ARGUMENT,):
+        raise ValueError(message)
+    if status in (cabi.STATUS_CUDA_ERROR, cabi.STATUS_DEVICE_TIMEOUT, cabi.STATUS_WORKSPACE_TOO_SMALL):
+        raise RuntimeError(message)
+    from ..._errors import OOpsUnsupportedError
+
+    raise OOpsUnsupportedError(message)
+
+
+def _split_lse(lse: Tensor, sizes: Sequence[Tuple[int, int, int, int]]) -> List[Tensor]:
+    pieces, at = [], 0
+    for size in sizes:
+        count = size[0] * size[1] * size[2] * size[3]
+        pieces.append(lse[at : at + count])
+        at += count
+    return pieces
+
+
+def run_forward(
+    geometry, query: Tensor, key: Tensor, value: Tensor, mask: Optional[Tensor], bias: Optional[Tensor], scale: float,
+    flags: int, want_lse: bool,
+) -> Tuple[Tensor, Optional[Tensor]]:
+    """Launch the forward pass of every view; returns ``(out, lse)``."""
+    lib = cabi.library()
+    device = query.device
+    out = torch.empty_like(query)
+    if out.shape[-1] != 1 and out.stride(-1) != 1:
+        out = torch.empty(query.shape, dtype=query.dtype, device=device)
+    sizes = geometry.lse_sizes(query)
+    lse = None
+    if want_lse:
+        lse = torch.empty(sum(b * r * h * c for b, r, h, c in sizes), dtype=torch.float32, device=device)
+    lse_views = _split_lse(lse, sizes) if lse is not None else [None] * len(sizes)
+    q_views, k_views, v_views = geometry.pair_views(query), geometry.pair_views(key), geometry.pair_views(value)
+    o_views = geometry.pair_views(out)
+    m_views = geometry.mask_views(mask) if mask is not None else [None] * len(q_views)
+    b_views = geometry.bias_views(bias) if bias is not None else [None] * len(q_views)
+    with torch.cuda.device(device):
+        stream = _current_stream_handle(device)
+        for q, k, v, o, m, b, l in zip(q_views, k_views, v_views, o_views, m_views, b_views, lse_views):
+            problem = cabi.make_problem(q, k, v, m, b, scale, flags)
+            status = lib.oops_ta_supported(cabi.byref(problem))
+            if status:
+                _raise_status(status, "forward")
+            scratch = _workspace(lib.oops_ta_forward_workspace_bytes(cabi.byref(problem)), device)
+            if scratch is not None:
+                problem.workspace = scratch.data_ptr()
+                problem.workspace_bytes = scratch.numel()
+            out_pair = cabi.pair_of(o)
+            status = lib.oops_ta_forward(
+                cabi.byref(problem), cabi.byref(out_pair), None if l is None else l.data_ptr(), stream
+            )
+            if status:
+                _raise_status(status, "forward")
+    return out, lse
+
+
+def run_backward(
+    geometry, grad_out: Tensor, query: Tensor, key: Tensor, value: Tensor, mask: Optional[Tensor],
+    bias: Optional[Tensor], out: Tensor, lse: Tensor, scale: float, flags: int, need: Sequence[bool],
+) -> Tuple[Optional[Tensor], Optional[Tensor], Optional[Tensor], Optional[Tensor]]:
+    """Launch the reverse pass of every view; returns ``(dq, dk, dv, dbias)``."""
+    lib = cabi.library()
+    device = query.device
+    need_q, need_k, need_v, need_b = need
+    need_b = need_b and bias is not None
+
+    def like(t: Tensor) -> Tensor:
+        g = torch.empty_like(t)
+        if g.shape[-1] != 1 and g.stride(-1) != 1:
+            g = torch.empty(t.shape, dtype=t.dtype, device=device)
+        return g
+
+    dq = like(query) if need_q else None
+    dk = like(key) if need_k else None
+    dv = like(value) if need_v else None
+    dbias = torch.empty(bias.shape, dtype=bias.dtype, device=device) if need_b else None
+
+    sizes = geometry.lse_sizes(query)
+    lse_views = _split_lse(lse, sizes)
+    count = len(sizes)
+    views = lambda t: geometry.pair_views(t) if t is not None else [None] * count  # noqa: E731
+    q_views, k_views, v_views = views(query), views(key), views(value)
+    o_views, do_views = views(out), views(grad_out)
+    dq_views, dk_views, dv_views = views(dq), views(dk), views(dv)
+    m_views = geometry.mask_views(mask) if mask is not None else [None] * count
+    b_views = geometry.bias_views(bias) if bias is not None else [None] * count
+    db_views = geometry.bias_views(dbias) if dbias is not None else [None] * count
+    with torch.cuda.device(device):
+        stream = _current_stream_handle(device)
+        for i in range(count):
+            problem = cabi.make_problem(q_views[i], k_views[i], v_views[i], m_views[i], b_views[i], scale, flags)
+            grads = cabi.Grads()
+            grads.dq, grads.dk, grads.dv = (cabi.pair_of(dq_views[i]), cabi.pair_of(dk_views[i]),
+                                            cabi.pair_of(dv_views[i]))
+            if db_views[i] is not None:
+                grads.dbias = db_views[i].data_ptr()
+                (grads.dbias_sb, grads.dbias_sg, grads.dbias_sh, grads.dbias_sq, grads.dbias_sk) = db_views[i].stride()
+            scratch = _workspace(lib.oops_ta_backward_workspace_bytes(cabi.byref(problem), cabi.byref(grads)), device)
+            if scratch is not None:
+                problem.workspace = scratch.data_ptr()
+                problem.workspace_bytes = scratch.numel()
+            out_pair, dout_pair = cabi.pair_of(o_views[i]), cabi.pair_of(do_views[i])
+            status = lib.oops_ta_backward(
+                cabi.byref(problem), cabi.byref(out_pair), cabi.byref(dout_pair), lse_views[i].data_ptr(),
+                cabi.byref(grads), stream,
+            )
+            if status:
+                _raise_status(status, "backward")
+    return dq, dk, dv, dbias
+
+
+class TriangleAttentionFunction(torch.autograd.Function):
+    """``out = f(query, key, value, mask, bias)`` with a hand-written reverse pass."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, mask, bias, scale, geometry, flags):
+        needs_grad = any(ctx.needs_input_grad[i] for i in (0, 1, 2, 4))
+        out, lse = run_forward(geometry, query, key, value, mask, bias, scale, flags, want_lse=needs_grad)
+        ctx.set_materialize_grads(False)
+        if needs_grad:
+            ctx.save_for_backward(query, key, value, mask, bias, out, lse)
+            ctx.scale, ctx.geometry, ctx.flags = scale, geometry, flags
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if grad_out is None:
+            return (None,) * 8
+        query, key, value, mask, bias, out, lse = ctx.saved_tensors
+        geometry = ctx.geometry
+        # Saved-tensor hooks may hand back copies with other strides; the views are rebuilt from what arrives.
+        query, key, value, out = (geometry.canonical_pair(t) for t in (query, key, value, out))
+        grad_out = geometry.canonical_pair(grad_out.resolve_neg().to(query.dtype))
+        if bias is not None:
+            bias = geometry.canonical_bias(bias)
+        if mask is not None and not isinstance(geometry, DenseGeometry):
+            mask = mask.contiguous()
+        lse = lse.contiguous()
+        need = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2], ctx.needs_input_grad[4])
+        dq, dk, dv, dbias = run_backward(
+            geometry, grad_out, query, key, value, mask, bias, out, lse, ctx.scale, ctx.flags, need
+        )
+        return dq, dk, dv, None, dbias, None, None, None
+
+
+def apply(query, key, value, mask, bias, scale, geometry, flags=0) -> Tensor:
+    return TriangleAttentionFunction.apply(query, key, value, mask, bias, scale, geometry, flags)

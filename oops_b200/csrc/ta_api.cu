@@ -1,0 +1,163 @@
+// C ABI of liboops_ta_sm100.so: argument checks, kernel selection, error text.
+// Declarations and the reference functions each entry point replaces are in
+// include/oops_ta.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "ta_internal.h"
+
+namespace oops_ta {
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+}  // namespace
+
+int fail(int status, const char* format, ...) {
+  va_list args;
+  va_start(args, format);
+  vsnprintf(g_error, sizeof(g_error), format, args);
+  va_end(args);
+  return status;
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int check_launch(const char* what) {
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(OOPS_TA_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(err));
+  return OOPS_TA_OK;
+}
+
+size_t dtype_size(int dtype) { return dtype == OOPS_TA_F32 ? 4 : 2; }
+
+namespace {
+
+bool valid_dtype(int d) { return d == OOPS_TA_F32 || d == OOPS_TA_F16 || d == OOPS_TA_BF16; }
+
+int validate(const oops_ta_problem* p, bool need_pointers) {
+  if (!p) return fail(OOPS_TA_INVALID_ARGUMENT, "problem is NULL");
+  if (p->abi_version != OOPS_TA_ABI_VERSION)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "ABI version %u, library has %d", p->abi_version, OOPS_TA_ABI_VERSION);
+  if (!valid_dtype(p->dtype)) return fail(OOPS_TA_UNSUPPORTED_DTYPE, "q/k/v dtype %d is not f32/f16/bf16", p->dtype);
+  if (p->batch <= 0 || p->rows <= 0 || p->cols <= 0 || p->heads <= 0)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "empty dimension (batch=%d rows=%d cols=%d heads=%d)", p->batch, p->rows,
+                p->cols, p->heads);
+  if (p->head_dim < 1 || p->head_dim > 256)
+    return fail(OOPS_TA_UNSUPPORTED_HEAD_DIM, "head_dim %d outside [1, 256]", p->head_dim);
+  if (p->bias_groups != 0) {
+    if (p->bias_groups != 1 && p->bias_groups != p->rows)
+      return fail(OOPS_TA_INVALID_ARGUMENT, "bias_groups %d must be 0, 1 or rows=%d", p->bias_groups, p->rows);
+    if (!valid_dtype(p->bias_dtype) || (p->bias_dtype != p->dtype && p->bias_dtype != OOPS_TA_F32))
+      return fail(OOPS_TA_UNSUPPORTED_DTYPE, "bias dtype %d must equal the q/k/v dtype or be f32", p->bias_dtype);
+    if (need_pointers && !p->bias) return fail(OOPS_TA_INVALID_ARGUMENT, "bias_groups set but bias is NULL");
+  }
+  if (need_pointers && (!p->q.ptr || !p->k.ptr || !p->v.ptr))
+    return fail(OOPS_TA_INVALID_ARGUMENT, "q, k or v is NULL");
+  const int64_t problems = int64_t(p->batch) * p->rows * p->heads;
+  if (problems > 0x7fffffffll || int64_t(p->cols) * p->cols > 0x7fffffffll)
+    return fail(OOPS_TA_LIMIT_EXCEEDED, "batch*rows*heads=%lld or cols^2 exceeds 2^31-1", (long long)problems);
+  return OOPS_TA_OK;
+}
+
+bool force_generic(const oops_ta_problem* p) { return (p->flags & OOPS_TA_FLAG_FORCE_GENERIC) != 0; }
+
+int check_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return fail(OOPS_TA_CUDA_ERROR, "cudaGetDevice failed");
+  static thread_local int cached_device = -1, cached_major = 0;
+  if (cached_device != device) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess)
+      return fail(OOPS_TA_CUDA_ERROR, "cudaDeviceGetAttribute failed");
+    cached_device = device;
+    cached_major = major;
+  }
+  if (cached_major != 10)
+    return fail(OOPS_TA_WRONG_DEVICE, "device %d has compute capability %d.x; this library is sm_100a only", device,
+                cached_major);
+  return OOPS_TA_OK;
+}
+
+}  // namespace
+}  // namespace oops_ta
+
+using namespace oops_ta;
+
+extern "C" {
+
+int oops_ta_abi_version(void) { return OOPS_TA_ABI_VERSION; }
+
+const char* oops_ta_status_string(int status) {
+  switch (status) {
+    case OOPS_TA_OK: return "ok";
+    case OOPS_TA_INVALID_ARGUMENT: return "invalid argument";
+    case OOPS_TA_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    case OOPS_TA_UNSUPPORTED_HEAD_DIM: return "unsupported head size";
+    case OOPS_TA_UNSUPPORTED_LAYOUT: return "unsupported layout";
+    case OOPS_TA_LIMIT_EXCEEDED: return "launch limit exceeded";
+    case OOPS_TA_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case OOPS_TA_CUDA_ERROR: return "CUDA error";
+    case OOPS_TA_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case OOPS_TA_WRONG_DEVICE: return "not an sm_100 device";
+    default: return "unknown status";
+  }
+}
+
+const char* oops_ta_last_error(void) { return g_error; }
+
+int oops_ta_supported(const oops_ta_problem* problem) { return validate(problem, false); }
+
+int oops_ta_uses_tensor_path(const oops_ta_problem* problem, int backward) {
+  const int status = validate(problem, false);
+  if (status) return -status;
+  if (force_generic(problem)) return 0;
+  return backward ? (tensor_backward_applies(*problem, nullptr) ? 1 : 0) : (tensor_forward_applies(*problem) ? 1 : 0);
+}
+
+uint64_t oops_ta_forward_workspace_bytes(const oops_ta_problem* problem) {
+  if (validate(problem, false)) return 0;
+  if (!force_generic(problem) && tensor_forward_applies(*problem)) return tensor_forward_workspace(*problem);
+  return generic_forward_workspace(*problem);
+}
+
+uint64_t oops_ta_backward_workspace_bytes(const oops_ta_problem* problem, const oops_ta_grads* grads) {
+  if (validate(problem, false) || !grads) return 0;
+  if (!force_generic(problem) && tensor_backward_applies(*problem, grads))
+    return tensor_backward_workspace(*problem, *grads);
+  return generic_backward_workspace(*problem, *grads);
+}
+
+int oops_ta_forward(const oops_ta_problem* problem, const oops_ta_pair* out, float* lse, void* stream) {
+  int status = validate(problem, true);
+  if (status) return status;
+  if (!out || !out->ptr) return fail(OOPS_TA_INVALID_ARGUMENT, "out is NULL");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!force_generic(problem) && tensor_forward_applies(*problem)) return tensor_forward(*problem, *out, lse, s);
+  return generic_forward(*problem, *out, lse, s);
+}
+
+int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, const oops_ta_pair* dout,
+                     const float* lse, const oops_ta_grads* grads, void* stream) {
+  int status = validate(problem, true);
+  if (status) return status;
+  if (!out || !out->ptr || !dout || !dout->ptr || !lse || !grads)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "out, dout, lse or grads is NULL");
+  if (grads->dbias && problem->bias_groups == 0)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "dbias requested but the problem has no bias");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!force_generic(problem) && tensor_backward_applies(*problem, grads))
+    return tensor_backward(*problem, *out, *dout, lse, *grads, s);
+  return generic_backward(*problem, *out, *dout, lse, *grads, s);
+}
+
+uint64_t oops_ta_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

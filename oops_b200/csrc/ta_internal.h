@@ -1,0 +1,40 @@
+// Internal declarations shared by the translation units of liboops_ta_sm100.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "oops_ta.h"
+
+namespace oops_ta {
+
+// Records a message for oops_ta_last_error() and returns `status`.
+int fail(int status, const char* format, ...);
+
+// Bumps the process-wide launch counter reported by oops_ta_launch_count().
+void count_launch(int n = 1);
+
+// Checks the last launch and converts a CUDA error into a status.
+int check_launch(const char* what);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+size_t dtype_size(int dtype);
+
+// Layout-agnostic FFMA kernels (any head_dim <= 256, any strides, f32/f16/bf16).
+uint64_t generic_forward_workspace(const oops_ta_problem& p);
+uint64_t generic_backward_workspace(const oops_ta_problem& p, const oops_ta_grads& g);
+int generic_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream);
+int generic_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
+                     const oops_ta_grads& g, cudaStream_t stream);
+
+// tcgen05/TMEM/TMA kernels (f16/bf16, head_dim 32, 16-byte aligned rows).
+bool tensor_forward_applies(const oops_ta_problem& p);
+bool tensor_backward_applies(const oops_ta_problem& p, const oops_ta_grads* g);
+uint64_t tensor_forward_workspace(const oops_ta_problem& p);
+uint64_t tensor_backward_workspace(const oops_ta_problem& p, const oops_ta_grads& g);
+int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream);
+int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
+                    const oops_ta_grads& g, cudaStream_t stream);
+
+}  // namespace oops_ta
