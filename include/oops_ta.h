@@ -159,6 +159,14 @@ int oops_ta_forward(const oops_ta_problem* problem, const oops_ta_pair* out, flo
 int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, const oops_ta_pair* dout,
                      const float* lse, const oops_ta_grads* grads, void* stream);
 
+/*
+ * Device-side status of the current device: OOPS_TA_OK, or OOPS_TA_DEVICE_TIMEOUT if a kernel
+ * gave up a bounded wait since the last reset (its outputs are then undefined).  Unlike every
+ * other call this one synchronises with the device.  `reset` != 0 clears the word.
+ * No counterpart in the reference (Triton kernels have no device-side waits).
+ */
+int oops_ta_device_status(int reset);
+
 /* Number of kernels the library has launched in this process (all streams). */
 uint64_t oops_ta_launch_count(void);
 

@@ -32,7 +32,7 @@ LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "liboops_ta_sm100.so
 EXPORTS = (
     "oops_ta_abi_version", "oops_ta_status_string", "oops_ta_last_error", "oops_ta_supported",
     "oops_ta_uses_tensor_path", "oops_ta_forward_workspace_bytes", "oops_ta_backward_workspace_bytes",
-    "oops_ta_forward", "oops_ta_backward", "oops_ta_launch_count",
+    "oops_ta_forward", "oops_ta_backward", "oops_ta_launch_count", "oops_ta_device_status",
 )
 
 
@@ -95,6 +95,8 @@ def library() -> ctypes.CDLL:
     lib.oops_ta_backward.restype = c_int
     lib.oops_ta_backward.argtypes = [POINTER(Problem), POINTER(Pair), POINTER(Pair), c_void_p, POINTER(Grads), c_void_p]
     lib.oops_ta_launch_count.restype = c_uint64
+    lib.oops_ta_device_status.restype = c_int
+    lib.oops_ta_device_status.argtypes = [c_int]
     if lib.oops_ta_abi_version() != ABI_VERSION:
         raise RuntimeError(f"{LIB_PATH} has ABI {lib.oops_ta_abi_version()}, the binding expects {ABI_VERSION}")
     _lib = lib
@@ -145,11 +147,16 @@ def make_problem(
     return problem
 
 
+def device_status(reset: bool = True) -> int:
+    """Synchronise and return the device-side status word (0 = ok, 8 = a bounded wait gave up)."""
+    return int(library().oops_ta_device_status(1 if reset else 0))
+
+
 def launch_count() -> int:
     return int(library().oops_ta_launch_count())
 
 
 __all__ = [
     "ABI_VERSION", "EXPORTS", "LIB_PATH", "Pair", "Problem", "Grads", "library", "status_message", "pair_of",
-    "make_problem", "launch_count", "byref", "FLAG_FORCE_GENERIC", "FLAG_ALLOW_TF32", "DTYPE_CODE",
+    "make_problem", "launch_count", "device_status", "byref", "FLAG_FORCE_GENERIC", "FLAG_ALLOW_TF32", "DTYPE_CODE",
 ]
