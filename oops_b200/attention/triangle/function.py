@@ -44,7 +44,15 @@ class DenseGeometry:
         return [(batch, rows, heads, cols)]
 
     def canonical_pair(self, tensor: Tensor) -> Tensor:
-        return tensor if tensor.shape[-1] == 1 or tensor.stride(-1) == 1 else tensor.contiguous()
+        """Unit inner stride; 16-bit tensors additionally get 16-byte aligned rows, which the TMA kernels need."""
+        if tensor.shape[-1] != 1 and tensor.stride(-1) != 1:
+            return tensor.contiguous()
+        if tensor.element_size() == 2 and (
+            tensor.data_ptr() % 16 != 0
+            or any(size > 1 and (stride <= 0 or stride % 8 != 0) for size, stride in zip(tensor.shape[:-1], tensor.stride()[:-1]))
+        ):
+            return tensor.contiguous()
+        return tensor
 
     def canonical_bias(self, bias: Tensor) -> Tensor:
         return bias

@@ -158,7 +158,11 @@ int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, co
   return generic_backward(*problem, *out, *dout, lse, *grads, s);
 }
 
-int oops_ta_device_status(int reset) { return device_status(reset); }
+int oops_ta_device_status(int reset) {
+  const int forward = forward_device_status(reset);
+  const int backward = backward_device_status(reset);
+  return forward ? forward : backward;
+}
 
 uint64_t oops_ta_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -37,7 +37,9 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
 int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
                     const oops_ta_grads& g, cudaStream_t stream);
 
-// Reads (and optionally clears) the device-side status word; synchronises with the device.
-int device_status(int reset);
+// Read (and optionally clear) the device-side status words of the two tcgen05 translation units;
+// both synchronise with the device.
+int forward_device_status(int reset);
+int backward_device_status(int reset);
 
 }  // namespace oops_ta

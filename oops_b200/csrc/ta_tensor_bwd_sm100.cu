@@ -1,0 +1,1120 @@
+// tcgen05 / TMEM / TMA reverse pass of triangle attention for sm_100a (f16 and bf16, head_dim 32).
+//
+// Replaces the reference's Triton kernels `_backward_preprocess`, `_backward_query`,
+// `_backward_key_value` and `_backward_shared_bias` (oops/attention/triangle/triton/kernel.py:374-873).
+// With P = exp(S - lse), dP = dO V^T, dS = P o (dP - delta) (kernel.py:499-564):
+//
+//   delta kernel     delta[q] = sum_d O[q,d] dO[q,d]                           (memory bound)
+//   dQ kernel        CTA = (batch,row,head, 2 query tiles), streams 64-key steps:
+//                    S = Q K^T, dP = dO V^T -> dS (16-bit, back into tensor memory) -> dQ += dS K.
+//                    A per-row bias gradient is dS itself and is stored from here.
+//   dK/dV kernel     CTA = (batch,row,head, 2 key tiles), streams 64-query steps, transposed:
+//                    S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T (tensor memory) -> dV += P^T dO, dK += dS^T Q.
+//                    It reads a transposed copy of the bias so that a thread (= one key) reads a bias row.
+//   shared-bias      CTA = (row part, batch, head, query tile, key tile) loops over its rows:
+//   gradient         S, dP -> dS accumulated in f32 registers over the rows (two warpgroups split the
+//                    128 keys), one f32 partial plane per part; a last kernel adds the parts in a fixed
+//                    order (no atomics, bitwise reproducible).
+//
+// All kernels share the forward kernel's structure: one TMA producer thread, one MMA-issuing thread,
+// two warpgroups of 128 threads that own one tensor-memory lane (= one query or key) each.
+#include "ta_tensor_common.cuh"
+
+namespace oops_ta {
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 320;
+constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
+constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
+constexpr int kSmallTile = kStep * kHeadDim * 2;        // 4 KiB: 64 x 32 tile
+constexpr int kBiasStep = kTile * kStep * 2;            // 16 KiB: 128 x 64 bias tile (one swizzle-128 box)
+constexpr int kRing = 4;                                // ring depth of the streamed operand pairs
+
+// ---------------------------------------------------------------------------------------------
+// small helper kernels
+// ---------------------------------------------------------------------------------------------
+
+template <typename T>
+__global__ void delta_kernel(oops_ta_pair out, oops_ta_pair dout, float* delta, int64_t total, int cols, int heads,
+                             int rows, int vec_ok) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int q = i % cols;
+  const int h = (i / cols) % heads;
+  const int r = (i / (int64_t(cols) * heads)) % rows;
+  const int64_t b = i / (int64_t(cols) * heads * rows);
+  const T* o = reinterpret_cast<const T*>(out.ptr) + b * out.sb + int64_t(r) * out.sr + int64_t(q) * out.sc + h * out.sh;
+  const T* d = reinterpret_cast<const T*>(dout.ptr) + b * dout.sb + int64_t(r) * dout.sr + int64_t(q) * dout.sc + h * dout.sh;
+  float total_dot = 0.f;
+  if (vec_ok) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 a = reinterpret_cast<const uint4*>(o)[c];
+      const uint4 g = reinterpret_cast<const uint4*>(d)[c];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        total_dot += Half2<T>::lo(aw[e]) * Half2<T>::lo(gw[e]) + Half2<T>::hi(aw[e]) * Half2<T>::hi(gw[e]);
+    }
+  } else {
+    for (int c = 0; c < kHeadDim; ++c) total_dot += float(o[c]) * float(d[c]);
+  }
+  delta[i] = total_dot;
+}
+
+// dst[z][k][q] = src[z][q][k] for 16-bit elements; dst rows are `dst_stride` elements apart.
+__global__ void transpose_bias_kernel(const uint16_t* src, uint16_t* dst, int cols, int64_t s_q, int64_t s_h, int64_t s_g,
+                                      int64_t s_b, int heads, int groups, int64_t dst_stride) {
+  __shared__ uint16_t tile[32][34];
+  const int z = blockIdx.z;
+  const int h = z % heads;
+  const int g = (z / heads) % groups;
+  const int64_t b = z / (heads * groups);
+  const uint16_t* plane = src + b * s_b + g * s_g + h * s_h;
+  uint16_t* out = dst + int64_t(z) * cols * dst_stride;
+  const int k0 = blockIdx.x * 32, q0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int q = q0 + i, k = k0 + threadIdx.x;
+    tile[i][threadIdx.x] = (q < cols && k < cols) ? plane[int64_t(q) * s_q + k] : uint16_t(0);
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int k = k0 + i, q = q0 + threadIdx.x;
+    if (k < cols && q < dst_stride) out[int64_t(k) * dst_stride + q] = q < cols ? tile[threadIdx.x][i] : uint16_t(0);
+  }
+}
+
+template <typename T>
+__global__ void reduce_parts_kernel(const float* parts, int num_parts, void* dbias, int64_t sb, int64_t sh, int64_t sq,
+                                    int64_t sk, int batch, int heads, int cols) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t plane = int64_t(batch) * heads * cols * cols;
+  if (i >= plane) return;
+  float total = 0.f;
+  for (int p = 0; p < num_parts; ++p) total += parts[int64_t(p) * plane + i];
+  const int k = i % cols;
+  const int q = (i / cols) % cols;
+  const int h = (i / (int64_t(cols) * cols)) % heads;
+  const int64_t b = i / (int64_t(cols) * cols * heads);
+  reinterpret_cast<T*>(dbias)[b * sb + h * sh + int64_t(q) * sq + int64_t(k) * sk] = T(total);
+}
+
+// 16-bit row store of 32 channels from f32 accumulator words, scaled.
+template <typename T>
+__device__ __forceinline__ void store_row32(T* dst, const uint32_t (&acc)[32], float scale, bool vec_ok) {
+  uint32_t o2[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    o2[i] = Half2<T>::pack(__uint_as_float(acc[2 * i]) * scale, __uint_as_float(acc[2 * i + 1]) * scale);
+  if (vec_ok) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d4[i] = make_uint4(o2[4 * i], o2[4 * i + 1], o2[4 * i + 2], o2[4 * i + 3]);
+  } else {
+    unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      d0[2 * i] = (unsigned short)(o2[i] & 0xffffu);
+      d0[2 * i + 1] = (unsigned short)(o2[i] >> 16);
+    }
+  }
+}
+
+__device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
+  return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && t.sb % 8 == 0 && t.sr % 8 == 0 && t.sc % 8 == 0 && t.sh % 8 == 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ kernel
+// ---------------------------------------------------------------------------------------------
+
+struct DqSmem {
+  static constexpr int q = 0;                                 // [2] 128 x 32
+  static constexpr int dout = q + 2 * kBigTile;               // [2] 128 x 32
+  static constexpr int kv = dout + 2 * kBigTile;              // [kRing] K step (4 KiB) + V step (4 KiB)
+  static constexpr int bias = kv + kRing * 2 * kSmallTile;    // [2 tiles][2 buffers] 128 x 64
+  static constexpr int bars = bias + 4 * kBiasStep;
+  static constexpr int qd_full = 0;                      // [2]
+  static constexpr int kv_full = qd_full + 2;            // [kRing]
+  static constexpr int kv_empty = kv_full + kRing;       // [kRing]
+  static constexpr int k_ready = kv_empty + kRing;       // [kRing]
+  static constexpr int bias_full = k_ready + kRing;      // [4]
+  static constexpr int bias_empty = bias_full + 4;       // [4]
+  static constexpr int sd_full = bias_empty + 4;         // [2]
+  static constexpr int ds_full = sd_full + 2;            // [2]
+  static constexpr int dq_done = ds_full + 2;            // [2]
+  static constexpr int num_bars = dq_done + 2;
+  static constexpr int tmem_slot = bars + num_bars * 8;
+  static constexpr int abort_flag = tmem_slot + 4;
+  static constexpr int total = abort_flag + 4;
+};
+constexpr int kDqSmemBytes = DqSmem::total + 1024;
+
+struct DqParams {
+  CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
+  oops_ta_pair dq;
+  const float* lse;
+  const float* delta;
+  const uint8_t* mask;
+  int64_t m_sb, m_sr, m_sc;
+  void* dbias_rows;  // per-row bias gradient (may be null)
+  int64_t db_sb, db_sg, db_sh, db_sq, db_sk;
+  int batch, rows, cols, heads, bias_groups;
+  int q_pairs, k_steps;
+  int write_dq;
+  float scale;
+};
+
+template <typename T, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_constant__ DqParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DqSmem::abort_flag);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DqSmem::tmem_slot);
+  auto bar = [&](int index) -> uint32_t { return smem_base + DqSmem::bars + index * 8; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int idx = blockIdx.x;
+  const int qp = idx % P.q_pairs;
+  idx /= P.q_pairs;
+  const int h = idx % P.heads;
+  idx /= P.heads;
+  const int r = idx % P.rows;
+  const int b = idx / P.rows;
+  const int q0 = qp * 2 * kTile;
+  const int n_tiles = (q0 + kTile < P.cols) ? 2 : 1;
+  const int KS = P.k_steps;
+  const int g = P.bias_groups == 1 ? 0 : r;
+  const bool has_mask = P.mask != nullptr;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DqSmem::qd_full + i), 1);
+      mbar_init(bar(DqSmem::sd_full + i), 1);
+      mbar_init(bar(DqSmem::ds_full + i), kTile);
+      mbar_init(bar(DqSmem::dq_done + i), 1);
+    }
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar(DqSmem::kv_full + i), 1);
+      mbar_init(bar(DqSmem::kv_empty + i), 1);
+      mbar_init(bar(DqSmem::k_ready + i), kTile);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(DqSmem::bias_full + i), 1);
+      mbar_init(bar(DqSmem::bias_empty + i), kTile);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_base + DqSmem::tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int w = 0; w < n_tiles; ++w) {
+        mbar_expect_tx(bar(DqSmem::qd_full + w), 2 * kBigTile);
+        tma_load_5d(smem_base + DqSmem::q + w * kBigTile, &P.map_q, bar(DqSmem::qd_full + w), 0, h, q0 + w * kTile, r, b);
+        tma_load_5d(smem_base + DqSmem::dout + w * kBigTile, &P.map_dout, bar(DqSmem::qd_full + w), 0, h, q0 + w * kTile, r, b);
+      }
+      for (int j = 0; j < KS && ok; ++j) {
+        const int st = j % kRing, round = j / kRing;
+        if (j >= kRing) ok = mbar_wait(bar(DqSmem::kv_empty + st), (round - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bar(DqSmem::kv_full + st), 2 * kSmallTile);
+        const uint32_t dst = smem_base + DqSmem::kv + st * 2 * kSmallTile;
+        tma_load_5d(dst, &P.map_k, bar(DqSmem::kv_full + st), 0, h, j * kStep, r, b);
+        tma_load_5d(dst + kSmallTile, &P.map_v, bar(DqSmem::kv_full + st), 0, h, j * kStep, r, b);
+        if (HAS_BIAS) {
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            const int slot = w * 2 + (j & 1);
+            if (j >= 2) ok = mbar_wait(bar(DqSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            mbar_expect_tx(bar(DqSmem::bias_full + slot), kBiasStep);
+            tma_load_5d(smem_base + DqSmem::bias + slot * kBiasStep, &P.map_bias, bar(DqSmem::bias_full + slot), j * kStep,
+                        q0 + w * kTile, h, g, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t fmt = Half2<T>::kFormat;
+      constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
+      constexpr uint32_t idesc_dq = instr_desc(fmt, 0, 1, kTile, kHeadDim);
+      const uint32_t ready_base = has_mask ? DqSmem::k_ready : DqSmem::kv_full;
+      bool ok = true;
+      for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
+      for (int j = 0; j <= KS && ok; ++j) {
+        if (j < KS) ok = mbar_wait(bar(ready_base + j % kRing), (j / kRing) & 1, abort_flag);
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          const uint32_t s_t = tmem_base + w * kTile;
+          const uint32_t dp_t = s_t + kStep;
+          const uint32_t dq_t = tmem_base + 2 * kTile + w * kHeadDim;
+          if (j > 0) {
+            const int jj = j - 1, st = jj % kRing;
+            ok = mbar_wait(bar(DqSmem::ds_full + w), jj & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
+            const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
+#pragma unroll
+            for (int kk = 0; kk < kStep / 16; ++kk)
+              mma_ts(dq_t, s_t + kk * 8, kdesc + uint64_t(kk * (1024 >> 4)), idesc_dq, (jj > 0 || kk > 0) ? 1u : 0u);
+            if (jj == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
+            if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
+          }
+          if (j < KS) {
+            const int st = j % kRing;
+            tc_fence_after_sync();
+            const uint32_t kv = smem_base + DqSmem::kv + st * 2 * kSmallTile;
+            const uint64_t qdesc = smem_desc(smem_base + DqSmem::q + w * kBigTile, 16, 512, kSwizzle64B);
+            const uint64_t ddesc = smem_desc(smem_base + DqSmem::dout + w * kBigTile, 16, 512, kSwizzle64B);
+            const uint64_t kdesc = smem_desc(kv, 16, 512, kSwizzle64B);
+            const uint64_t vdesc = smem_desc(kv + kSmallTile, 16, 512, kSwizzle64B);
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk)
+              mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk)
+              mma_ss(dp_t, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+            mma_commit(bar(DqSmem::sd_full + w));
+          }
+        }
+      }
+    }
+  } else if ((warp >> 2) < n_tiles) {
+    const int w = warp >> 2;
+    const int t = tid & (kTile - 1);
+    const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t s_t = tmem_base + lane_field + w * kTile;
+    const uint32_t dp_t = s_t + kStep;
+    const uint32_t dq_t = tmem_base + lane_field + 2 * kTile + w * kHeadDim;
+    const int q_index = q0 + w * kTile + t;
+    const bool q_valid = q_index < P.cols;
+    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+    const int64_t stat_at = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index;
+    const float neg_lse2 = q_valid ? -P.lse[stat_at] * kLog2e : -INFINITY;
+    const float delta = q_valid ? P.delta[stat_at] : 0.f;
+    const float scale = P.scale;
+    T* db_row = nullptr;
+    bool db_vec = false;
+    if (P.dbias_rows && q_valid) {
+      db_row = reinterpret_cast<T*>(P.dbias_rows) + b * P.db_sb + int64_t(r) * P.db_sg + h * P.db_sh + int64_t(q_index) * P.db_sq;
+      db_vec = P.db_sk == 1 && (reinterpret_cast<uintptr_t>(db_row) & 15) == 0;
+    }
+    bool ok = true;
+
+    for (int j = 0; j < KS && ok; ++j) {
+      uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
+      const bool need_bits = has_mask || (j == KS - 1 && (P.cols % kStep) != 0);
+      if (need_bits) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int key = j * kStep + i * 32 + lane;
+          bool keep = key < P.cols;
+          if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+          bits[i] = __ballot_sync(0xffffffffu, keep);
+        }
+      }
+      const bool all_kept = (bits[0] & bits[1]) == 0xffffffffu;
+      if (has_mask && w == 0) {
+        // Key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory.
+        const int st = j % kRing;
+        ok = mbar_wait(bar(DqSmem::kv_full + st), (j / kRing) & 1, abort_flag);
+        if (!ok) break;
+        if (!all_kept && t < kStep && ((bits[t >> 5] >> (t & 31)) & 1u) == 0) {
+          uint4* row = reinterpret_cast<uint4*>(smem_gen + DqSmem::kv + st * 2 * kSmallTile + t * 64);
+          row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar(DqSmem::k_ready + st));
+      }
+      ok = mbar_wait(bar(DqSmem::sd_full + w), j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int slot = w * 2 + (j & 1);
+      if (HAS_BIAS) {
+        ok = mbar_wait(bar(DqSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128;
+      uint32_t packed[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sraw[32], draw[32];
+        tmem_ld32(s_t + c * 32, sraw);
+        tmem_ld32(dp_t + c * 32, draw);
+        tmem_wait_ld();
+        float ds[32];
+#pragma unroll
+        for (int i8 = 0; i8 < 4; ++i8) {
+          float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (HAS_BIAS) {
+            const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
+            bv[0] = Half2<T>::lo(v.x); bv[1] = Half2<T>::hi(v.x); bv[2] = Half2<T>::lo(v.y); bv[3] = Half2<T>::hi(v.y);
+            bv[4] = Half2<T>::lo(v.z); bv[5] = Half2<T>::hi(v.z); bv[6] = Half2<T>::lo(v.w); bv[7] = Half2<T>::hi(v.w);
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int i = i8 * 8 + e;
+            const float x = fmaf(__uint_as_float(sraw[i]), scale, bv[e]);
+            const float p = ex2(fmaf(x, kLog2e, neg_lse2));
+            ds[i] = p * (__uint_as_float(draw[i]) - delta);
+          }
+        }
+        if (!all_kept) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (((bits[c] >> i) & 1u) == 0) ds[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) packed[c * 16 + (i >> 1)] = Half2<T>::pack(ds[i], ds[i + 1]);
+        if (db_row) {
+          const int key0 = j * kStep + c * 32;
+          if (db_vec && key0 + 32 <= P.cols) {
+            uint4* d4 = reinterpret_cast<uint4*>(db_row + key0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              d4[i] = make_uint4(packed[c * 16 + 4 * i], packed[c * 16 + 4 * i + 1], packed[c * 16 + 4 * i + 2],
+                                 packed[c * 16 + 4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key0 + i < P.cols) db_row[int64_t(key0 + i) * P.db_sk] = T(ds[i]);
+          }
+        }
+      }
+      if (HAS_BIAS) mbar_arrive(bar(DqSmem::bias_empty + slot));
+      tmem_st32(s_t, packed);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(DqSmem::ds_full + w));
+    }
+
+    if (ok) ok = mbar_wait(bar(DqSmem::dq_done + w), 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      uint32_t acc[32];
+      tmem_ld32(dq_t, acc);
+      tmem_wait_ld();
+      if (q_valid && P.write_dq) {
+        T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
+        store_row32<T>(dst, acc, scale, pair_vec_ok(P.dq));
+      }
+    }
+  }
+  teardown(abort_flag, tmem_base, 9);
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK / dV kernel (transposed: a thread owns a key)
+// ---------------------------------------------------------------------------------------------
+
+struct DkvSmem {
+  static constexpr int k = 0;                                  // [2] 128 x 32
+  static constexpr int v = k + 2 * kBigTile;                   // [2] 128 x 32
+  static constexpr int qd = v + 2 * kBigTile;                  // [kRing] Q step (4 KiB) + dO step (4 KiB)
+  static constexpr int bias = qd + kRing * 2 * kSmallTile;     // [2 tiles][2 buffers] 128 keys x 64 queries
+  static constexpr int stats = bias + 4 * kBiasStep;           // [2 tiles][2 buffers][128 floats]: lse*log2e | delta
+  static constexpr int bars = stats + 4 * 512;
+  static constexpr int kv_full = 0;                      // [2]
+  static constexpr int qd_full = kv_full + 2;            // [kRing]
+  static constexpr int qd_empty = qd_full + kRing;       // [kRing]
+  static constexpr int bias_full = qd_empty + kRing;     // [4]
+  static constexpr int bias_empty = bias_full + 4;       // [4]
+  static constexpr int sd_full = bias_empty + 4;         // [2]
+  static constexpr int pds_full = sd_full + 2;           // [2]
+  static constexpr int done = pds_full + 2;              // [2]
+  static constexpr int num_bars = done + 2;
+  static constexpr int tmem_slot = bars + num_bars * 8;
+  static constexpr int abort_flag = tmem_slot + 4;
+  static constexpr int total = abort_flag + 4;
+};
+constexpr int kDkvSmemBytes = DkvSmem::total + 1024;
+
+struct DkvParams {
+  CUtensorMap map_k, map_v, map_q, map_dout, map_bias_t;
+  oops_ta_pair dk, dv;
+  const float* lse;
+  const float* delta;
+  const uint8_t* mask;
+  int64_t m_sb, m_sr, m_sc;
+  int batch, rows, cols, heads, bias_groups;
+  int k_pairs, q_steps;
+  int write_dk, write_dv;
+  float scale;
+};
+
+template <typename T, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_constant__ DkvParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DkvSmem::abort_flag);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DkvSmem::tmem_slot);
+  auto bar = [&](int index) -> uint32_t { return smem_base + DkvSmem::bars + index * 8; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int idx = blockIdx.x;
+  const int kp = idx % P.k_pairs;
+  idx /= P.k_pairs;
+  const int h = idx % P.heads;
+  idx /= P.heads;
+  const int r = idx % P.rows;
+  const int b = idx / P.rows;
+  const int k0 = kp * 2 * kTile;
+  const int n_tiles = (k0 + kTile < P.cols) ? 2 : 1;
+  const int QS = P.q_steps;
+  const int g = P.bias_groups == 1 ? 0 : r;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DkvSmem::kv_full + i), 1);
+      mbar_init(bar(DkvSmem::sd_full + i), 1);
+      mbar_init(bar(DkvSmem::pds_full + i), kTile);
+      mbar_init(bar(DkvSmem::done + i), 1);
+    }
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar(DkvSmem::qd_full + i), 1);
+      mbar_init(bar(DkvSmem::qd_empty + i), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(DkvSmem::bias_full + i), 1);
+      mbar_init(bar(DkvSmem::bias_empty + i), kTile);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_base + DkvSmem::tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr int kWgCols = 192;  // S^T 64 | dP^T 64 | dK 32 | dV 32 per key tile
+
+  if (warp == 8) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int w = 0; w < n_tiles; ++w) {
+        mbar_expect_tx(bar(DkvSmem::kv_full + w), 2 * kBigTile);
+        tma_load_5d(smem_base + DkvSmem::k + w * kBigTile, &P.map_k, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
+        tma_load_5d(smem_base + DkvSmem::v + w * kBigTile, &P.map_v, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
+      }
+      for (int j = 0; j < QS && ok; ++j) {
+        const int st = j % kRing, round = j / kRing;
+        if (j >= kRing) ok = mbar_wait(bar(DkvSmem::qd_empty + st), (round - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bar(DkvSmem::qd_full + st), 2 * kSmallTile);
+        const uint32_t dst = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
+        tma_load_5d(dst, &P.map_q, bar(DkvSmem::qd_full + st), 0, h, j * kStep, r, b);
+        tma_load_5d(dst + kSmallTile, &P.map_dout, bar(DkvSmem::qd_full + st), 0, h, j * kStep, r, b);
+        if (HAS_BIAS) {
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            const int slot = w * 2 + (j & 1);
+            if (j >= 2) ok = mbar_wait(bar(DkvSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            mbar_expect_tx(bar(DkvSmem::bias_full + slot), kBiasStep);
+            // transposed bias: inner axis = query, outer axis = key
+            tma_load_5d(smem_base + DkvSmem::bias + slot * kBiasStep, &P.map_bias_t, bar(DkvSmem::bias_full + slot),
+                        j * kStep, k0 + w * kTile, h, g, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t fmt = Half2<T>::kFormat;
+      constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
+      constexpr uint32_t idesc_acc = instr_desc(fmt, 0, 1, kTile, kHeadDim);
+      bool ok = true;
+      for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
+      for (int j = 0; j <= QS && ok; ++j) {
+        if (j < QS) ok = mbar_wait(bar(DkvSmem::qd_full + j % kRing), (j / kRing) & 1, abort_flag);
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          const uint32_t st_t = tmem_base + w * kWgCols;
+          const uint32_t dpt_t = st_t + kStep;
+          const uint32_t dk_t = st_t + 2 * kStep;
+          const uint32_t dv_t = dk_t + kHeadDim;
+          if (j > 0) {
+            const int jj = j - 1, st = jj % kRing;
+            ok = mbar_wait(bar(DkvSmem::pds_full + w), jj & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
+            const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);                 // Q step, MN-major
+            const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);    // dO step, MN-major
+#pragma unroll
+            for (int kk = 0; kk < kStep / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 64 q] dO[64 q x 32]
+              mma_ts(dv_t, st_t + kk * 8, ddesc + uint64_t(kk * (1024 >> 4)), idesc_acc, (jj > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < kStep / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 64 q] Q[64 q x 32]
+              mma_ts(dk_t, dpt_t + kk * 8, qdesc + uint64_t(kk * (1024 >> 4)), idesc_acc, (jj > 0 || kk > 0) ? 1u : 0u);
+            if (jj == QS - 1) mma_commit(bar(DkvSmem::done + w));
+            if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
+          }
+          if (j < QS) {
+            const int st = j % kRing;
+            tc_fence_after_sync();
+            const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
+            const uint64_t kdesc = smem_desc(smem_base + DkvSmem::k + w * kBigTile, 16, 512, kSwizzle64B);
+            const uint64_t vdesc = smem_desc(smem_base + DkvSmem::v + w * kBigTile, 16, 512, kSwizzle64B);
+            const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);
+            const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk)  // S^T[128 k x 64 q] = K Q^T
+              mma_ss(st_t, kdesc + uint64_t(kk * 2), qdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk)  // dP^T[128 k x 64 q] = V dO^T
+              mma_ss(dpt_t, vdesc + uint64_t(kk * 2), ddesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+            mma_commit(bar(DkvSmem::sd_full + w));
+          }
+        }
+      }
+    }
+  } else if ((warp >> 2) < n_tiles) {
+    const int w = warp >> 2;
+    const int t = tid & (kTile - 1);
+    const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t st_t = tmem_base + lane_field + w * kWgCols;
+    const uint32_t dpt_t = st_t + kStep;
+    const uint32_t dk_t = st_t + 2 * kStep;
+    const uint32_t dv_t = dk_t + kHeadDim;
+    const int key = k0 + w * kTile + t;
+    bool keep = key < P.cols;
+    if (keep && P.mask) keep = P.mask[b * P.m_sb + int64_t(r) * P.m_sr + int64_t(key) * P.m_sc] != 0;
+    const float scale = P.scale;
+    const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
+    bool ok = true;
+
+    for (int j = 0; j < QS && ok; ++j) {
+      // stage this step's 64 (lse*log2e, delta) pairs for the warpgroup
+      float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (w * 2 + (j & 1)) * 512);
+      {
+        const int q = j * kStep + (t & 63);
+        float value;
+        if (t < 64) value = q < P.cols ? -P.lse[stat_base + q] * kLog2e : -INFINITY;
+        else value = q < P.cols ? P.delta[stat_base + q] : 0.f;
+        stats[t] = value;
+      }
+      named_barrier_sync(1 + w, kTile);
+      ok = mbar_wait(bar(DkvSmem::sd_full + w), j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int slot = w * 2 + (j & 1);
+      if (HAS_BIAS) {
+        ok = mbar_wait(bar(DkvSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128;
+      uint32_t p_packed[32], ds_packed[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sraw[32], draw[32];
+        tmem_ld32(st_t + c * 32, sraw);
+        tmem_ld32(dpt_t + c * 32, draw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i8 = 0; i8 < 4; ++i8) {
+          float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (HAS_BIAS) {
+            const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
+            bv[0] = Half2<T>::lo(v.x); bv[1] = Half2<T>::hi(v.x); bv[2] = Half2<T>::lo(v.y); bv[3] = Half2<T>::hi(v.y);
+            bv[4] = Half2<T>::lo(v.z); bv[5] = Half2<T>::hi(v.z); bv[6] = Half2<T>::lo(v.w); bv[7] = Half2<T>::hi(v.w);
+          }
+          const float4 l0 = *reinterpret_cast<const float4*>(stats + c * 32 + i8 * 8);
+          const float4 l1 = *reinterpret_cast<const float4*>(stats + c * 32 + i8 * 8 + 4);
+          const float4 d0 = *reinterpret_cast<const float4*>(stats + 64 + c * 32 + i8 * 8);
+          const float4 d1 = *reinterpret_cast<const float4*>(stats + 64 + c * 32 + i8 * 8 + 4);
+          const float nl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+          const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+          float pv[8], dv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int i = i8 * 8 + e;
+            const float x = fmaf(__uint_as_float(sraw[i]), scale, bv[e]);
+            const float p = keep ? ex2(fmaf(x, kLog2e, nl[e])) : 0.f;
+            pv[e] = p;
+            dv[e] = keep ? p * (__uint_as_float(draw[i]) - dl[e]) : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            p_packed[c * 16 + i8 * 4 + (e >> 1)] = Half2<T>::pack(pv[e], pv[e + 1]);
+            ds_packed[c * 16 + i8 * 4 + (e >> 1)] = Half2<T>::pack(dv[e], dv[e + 1]);
+          }
+        }
+      }
+      if (HAS_BIAS) mbar_arrive(bar(DkvSmem::bias_empty + slot));
+      tmem_st32(st_t, p_packed);
+      tmem_st32(dpt_t, ds_packed);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar(DkvSmem::pds_full + w));
+    }
+
+    if (ok) ok = mbar_wait(bar(DkvSmem::done + w), 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      uint32_t acc[32];
+      if (P.write_dk) {
+        tmem_ld32(dk_t, acc);
+        tmem_wait_ld();
+        if (key < P.cols) {
+          T* dst = reinterpret_cast<T*>(P.dk.ptr) + b * P.dk.sb + int64_t(r) * P.dk.sr + int64_t(key) * P.dk.sc + h * P.dk.sh;
+          store_row32<T>(dst, acc, scale, pair_vec_ok(P.dk));
+        }
+      }
+      if (P.write_dv) {
+        tmem_ld32(dv_t, acc);
+        tmem_wait_ld();
+        if (key < P.cols) {
+          T* dst = reinterpret_cast<T*>(P.dv.ptr) + b * P.dv.sb + int64_t(r) * P.dv.sr + int64_t(key) * P.dv.sc + h * P.dv.sh;
+          store_row32<T>(dst, acc, 1.f, pair_vec_ok(P.dv));
+        }
+      }
+    }
+  }
+  teardown(abort_flag, tmem_base, 9);
+}
+
+// ---------------------------------------------------------------------------------------------
+// shared-bias gradient kernel
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kDbRing = 3;
+struct DbSmem {
+  static constexpr int bias = 0;                                // 128 x 128 (two 64-key boxes)
+  static constexpr int ring = bias + 2 * kBiasStep;             // [kDbRing] Q | dO | K | V, 8 KiB each
+  static constexpr int bars = ring + kDbRing * 4 * kBigTile;
+  static constexpr int bias_full = 0;
+  static constexpr int row_full = 1;                     // [kDbRing]
+  static constexpr int row_empty = row_full + kDbRing;   // [kDbRing]
+  static constexpr int sd_full = row_empty + kDbRing;    // [2]
+  static constexpr int sd_free = sd_full + 2;            // [2]
+  static constexpr int num_bars = sd_free + 2;
+  static constexpr int tmem_slot = bars + num_bars * 8;
+  static constexpr int abort_flag = tmem_slot + 4;
+  static constexpr int total = abort_flag + 4;
+};
+constexpr int kDbSmemBytes = DbSmem::total + 1024;
+
+struct DbParams {
+  CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
+  float* parts;  // [parts][batch][heads][cols][cols] f32
+  const float* lse;
+  const float* delta;
+  const uint8_t* mask;
+  int64_t m_sb, m_sr, m_sc;
+  int batch, rows, cols, heads;
+  int tiles, num_parts, rows_per_part;
+  float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DbSmem::abort_flag);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DbSmem::tmem_slot);
+  auto bar = [&](int index) -> uint32_t { return smem_base + DbSmem::bars + index * 8; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int idx = blockIdx.x;
+  const int kt = idx % P.tiles;
+  idx /= P.tiles;
+  const int qt = idx % P.tiles;
+  idx /= P.tiles;
+  const int h = idx % P.heads;
+  idx /= P.heads;
+  const int b = idx % P.batch;
+  const int part = idx / P.batch;
+  const int row_lo = part * P.rows_per_part;
+  const int row_hi = min(P.rows, row_lo + P.rows_per_part);
+  const int n_rows = max(0, row_hi - row_lo);
+  const bool has_mask = P.mask != nullptr;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(DbSmem::bias_full), 1);
+    for (int i = 0; i < kDbRing; ++i) {
+      mbar_init(bar(DbSmem::row_full + i), 1);
+      mbar_init(bar(DbSmem::row_empty + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DbSmem::sd_full + i), 1);
+      mbar_init(bar(DbSmem::sd_free + i), 2 * kTile);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_base + DbSmem::tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(bar(DbSmem::bias_full), 2 * kBiasStep);
+      tma_load_5d(smem_base + DbSmem::bias, &P.map_bias, bar(DbSmem::bias_full), kt * kTile, qt * kTile, h, 0, b);
+      tma_load_5d(smem_base + DbSmem::bias + kBiasStep, &P.map_bias, bar(DbSmem::bias_full), kt * kTile + 64, qt * kTile, h, 0, b);
+      for (int i = 0; i < n_rows && ok; ++i) {
+        const int st = i % kDbRing, round = i / kDbRing, r = row_lo + i;
+        if (i >= kDbRing) ok = mbar_wait(bar(DbSmem::row_empty + st), (round - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bar(DbSmem::row_full + st), 4 * kBigTile);
+        const uint32_t dst = smem_base + DbSmem::ring + st * 4 * kBigTile;
+        tma_load_5d(dst, &P.map_q, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
+        tma_load_5d(dst + kBigTile, &P.map_dout, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
+        tma_load_5d(dst + 2 * kBigTile, &P.map_k, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
+        tma_load_5d(dst + 3 * kBigTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t fmt = Half2<T>::kFormat;
+      constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kTile);
+      bool ok = true;
+      for (int i = 0; i < n_rows && ok; ++i) {
+        const int st = i % kDbRing, buf = i & 1;
+        ok = mbar_wait(bar(DbSmem::row_full + st), (i / kDbRing) & 1, abort_flag);
+        if (ok && i >= 2) ok = mbar_wait(bar(DbSmem::sd_free + buf), ((i >> 1) - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t base = smem_base + DbSmem::ring + st * 4 * kBigTile;
+        const uint64_t qdesc = smem_desc(base, 16, 512, kSwizzle64B);
+        const uint64_t ddesc = smem_desc(base + kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t kdesc = smem_desc(base + 2 * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t vdesc = smem_desc(base + 3 * kBigTile, 16, 512, kSwizzle64B);
+        const uint32_t s_t = tmem_base + buf * 2 * kTile;
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(s_t + kTile, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+        mma_commit(bar(DbSmem::sd_full + buf));
+        mma_commit(bar(DbSmem::row_empty + st));
+      }
+    }
+  } else {
+    const int w = warp >> 2;  // key half
+    const int t = tid & (kTile - 1);
+    const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+    const int q_index = qt * kTile + t;
+    const bool q_valid = q_index < P.cols;
+    const int key_base = kt * kTile + w * kStep;
+    const float scale = P.scale;
+    float acc[kStep];
+#pragma unroll
+    for (int i = 0; i < kStep; ++i) acc[i] = 0.f;
+    bool ok = mbar_wait(bar(DbSmem::bias_full), 0, abort_flag);
+    const uint8_t* bias_row = smem_gen + DbSmem::bias + w * kBiasStep + t * 128;
+
+    for (int i = 0; i < n_rows && ok; ++i) {
+      const int r = row_lo + i, buf = i & 1;
+      const int64_t stat_at = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index;
+      const float neg_lse2 = q_valid ? -P.lse[stat_at] * kLog2e : -INFINITY;
+      const float delta = q_valid ? P.delta[stat_at] : 0.f;
+      uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
+      const bool need_bits = has_mask || key_base + kStep > P.cols;
+      if (need_bits) {
+        const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key = key_base + c * 32 + lane;
+          bool keep = key < P.cols;
+          if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+          bits[c] = __ballot_sync(0xffffffffu, keep);
+        }
+      }
+      ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + w * kStep;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sraw[32], draw[32];
+        tmem_ld32(s_t + c * 32, sraw);
+        tmem_ld32(s_t + kTile + c * 32, draw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i8 = 0; i8 < 4; ++i8) {
+          const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
+          const float bv[8] = {Half2<T>::lo(v.x), Half2<T>::hi(v.x), Half2<T>::lo(v.y), Half2<T>::hi(v.y),
+                               Half2<T>::lo(v.z), Half2<T>::hi(v.z), Half2<T>::lo(v.w), Half2<T>::hi(v.w)};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int n = i8 * 8 + e;
+            const float x = fmaf(__uint_as_float(sraw[n]), scale, bv[e]);
+            const float p = ex2(fmaf(x, kLog2e, neg_lse2));
+            const float ds = p * (__uint_as_float(draw[n]) - delta);
+            const bool kept = (bits[c] >> n) & 1u;
+            acc[c * 32 + n] += kept ? ds : 0.f;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(DbSmem::sd_free + buf));
+    }
+    if (ok && q_valid) {
+      float* dst = P.parts + (((int64_t(part) * P.batch + b) * P.heads + h) * P.cols + q_index) * P.cols + key_base;
+      if (key_base + kStep <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < kStep; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kStep; ++i)
+          if (key_base + i < P.cols) dst[i] = acc[i];
+      }
+    }
+  }
+  teardown(abort_flag, tmem_base, 9);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+
+uint64_t align256(uint64_t v) { return (v + 255) & ~uint64_t(255); }
+
+int64_t padded_cols(const oops_ta_problem& p) { return (int64_t(p.cols) + 7) & ~int64_t(7); }
+
+int bias_parts(const oops_ta_problem& p) {
+  const int64_t tiles = ceil_div(p.cols, kTile);
+  const int64_t ctas = int64_t(p.batch) * p.heads * tiles * tiles;
+  int64_t parts = ceil_div(4 * 148, ctas);
+  parts = std::max<int64_t>(1, std::min<int64_t>(parts, std::min<int64_t>(16, p.rows)));
+  return (int)parts;
+}
+
+struct Layout {
+  uint64_t delta, bias_t, parts, total;
+};
+
+Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
+  Layout l{};
+  uint64_t at = 0;
+  l.delta = at;
+  at += align256(uint64_t(p.batch) * p.rows * p.heads * p.cols * sizeof(float));
+  l.bias_t = at;
+  if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr))
+    at += align256(uint64_t(p.batch) * p.bias_groups * p.heads * p.cols * padded_cols(p) * 2);
+  l.parts = at;
+  if (g.dbias && p.bias_groups == 1)
+    at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
+  l.total = at;
+  return l;
+}
+
+template <typename T, typename Params, typename K1, typename K0>
+int launch_pair(bool has_bias, K1 with_bias, K0 without_bias, const Params& P, unsigned grid, int smem, cudaStream_t stream,
+                const char* what) {
+  auto go = [&](auto kernel) -> int {
+    const int rc = reserve_smem(kernel, smem);
+    if (rc) return rc;
+    kernel<<<grid, kThreads, smem, stream>>>(P);
+    count_launch();
+    return check_launch(what);
+  };
+  return has_bias ? go(with_bias) : go(without_bias);
+}
+
+template <typename T>
+int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
+                 const oops_ta_grads& g, cudaStream_t stream) {
+  const Layout layout = workspace_layout(p, g);
+  if (!p.workspace || p.workspace_bytes < layout.total)
+    return fail(OOPS_TA_WORKSPACE_TOO_SMALL, "backward needs %llu scratch bytes, got %llu", (unsigned long long)layout.total,
+                (unsigned long long)p.workspace_bytes);
+  char* base = reinterpret_cast<char*>(p.workspace);
+  float* delta = reinterpret_cast<float*>(base + layout.delta);
+  const bool has_bias = p.bias_groups != 0;
+  const bool row_bias_grad = g.dbias && p.bias_groups > 1;
+  const bool shared_bias_grad = g.dbias && p.bias_groups == 1;
+  int status;
+
+  {  // delta = rowsum(O * dO)
+    const int64_t total = int64_t(p.batch) * p.rows * p.heads * p.cols;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(out.ptr) & 15) == 0 && (reinterpret_cast<uintptr_t>(dout.ptr) & 15) == 0 &&
+                       out.sb % 8 == 0 && out.sr % 8 == 0 && out.sc % 8 == 0 && out.sh % 8 == 0 && dout.sb % 8 == 0 &&
+                       dout.sr % 8 == 0 && dout.sc % 8 == 0 && dout.sh % 8 == 0;
+    delta_kernel<T><<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(out, dout, delta, total, p.cols, p.heads, p.rows, vec_ok);
+    count_launch();
+    status = check_launch("tcgen05 delta");
+    if (status) return status;
+  }
+
+  CUtensorMap map_q128, map_d128, map_k128, map_v128;
+  if (g.dq.ptr || row_bias_grad) {
+    DqParams P{};
+    status = encode_pair(&P.map_q, p, p.q, kTile, "query");
+    if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
+    if (!status) status = encode_pair(&P.map_k, p, p.k, kStep, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kStep, "value");
+    if (!status && has_bias)
+      status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
+    if (status) return status;
+    P.dq = g.dq;
+    P.write_dq = g.dq.ptr != nullptr;
+    P.lse = lse;
+    P.delta = delta;
+    P.mask = p.mask;
+    P.m_sb = p.mask_sb;
+    P.m_sr = p.mask_sr;
+    P.m_sc = p.mask_sc;
+    if (row_bias_grad) {
+      P.dbias_rows = g.dbias;
+      P.db_sb = g.dbias_sb;
+      P.db_sg = g.dbias_sg;
+      P.db_sh = g.dbias_sh;
+      P.db_sq = g.dbias_sq;
+      P.db_sk = g.dbias_sk;
+    }
+    P.batch = p.batch;
+    P.rows = p.rows;
+    P.cols = p.cols;
+    P.heads = p.heads;
+    P.bias_groups = p.bias_groups;
+    P.q_pairs = (int)ceil_div(p.cols, 2 * kTile);
+    P.k_steps = (int)ceil_div(p.cols, kStep);
+    P.scale = p.scale;
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.q_pairs);
+    status = launch_pair<T>(has_bias, ta_bwd_dq_kernel<T, true>, ta_bwd_dq_kernel<T, false>, P, grid, kDqSmemBytes, stream,
+                            "tcgen05 dQ");
+    if (status) return status;
+  }
+
+  if (g.dk.ptr || g.dv.ptr) {
+    DkvParams P{};
+    status = encode_pair(&P.map_k, p, p.k, kTile, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
+    if (!status) status = encode_pair(&P.map_q, p, p.q, kStep, "query");
+    if (!status) status = encode_pair(&P.map_dout, p, dout, kStep, "upstream gradient");
+    if (status) return status;
+    if (has_bias) {
+      uint16_t* bias_t = reinterpret_cast<uint16_t*>(base + layout.bias_t);
+      const int64_t stride = padded_cols(p);
+      dim3 grid((unsigned)ceil_div(stride, 32), (unsigned)ceil_div(p.cols, 32), (unsigned)(p.batch * p.bias_groups * p.heads));
+      transpose_bias_kernel<<<grid, dim3(32, 8), 0, stream>>>(reinterpret_cast<const uint16_t*>(p.bias), bias_t, p.cols,
+                                                              p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, p.heads,
+                                                              p.bias_groups, stride);
+      count_launch();
+      status = check_launch("tcgen05 bias transpose");
+      if (status) return status;
+      const int64_t plane = int64_t(p.cols) * stride;
+      status = encode_bias(&P.map_bias_t, p, bias_t, stride, plane, plane * p.heads, plane * p.heads * p.bias_groups, kTile,
+                           "transposed bias");
+      if (status) return status;
+    }
+    P.dk = g.dk;
+    P.dv = g.dv;
+    P.write_dk = g.dk.ptr != nullptr;
+    P.write_dv = g.dv.ptr != nullptr;
+    P.lse = lse;
+    P.delta = delta;
+    P.mask = p.mask;
+    P.m_sb = p.mask_sb;
+    P.m_sr = p.mask_sr;
+    P.m_sc = p.mask_sc;
+    P.batch = p.batch;
+    P.rows = p.rows;
+    P.cols = p.cols;
+    P.heads = p.heads;
+    P.bias_groups = p.bias_groups;
+    P.k_pairs = (int)ceil_div(p.cols, 2 * kTile);
+    P.q_steps = (int)ceil_div(p.cols, kStep);
+    P.scale = p.scale;
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.k_pairs);
+    status = launch_pair<T>(has_bias, ta_bwd_dkv_kernel<T, true>, ta_bwd_dkv_kernel<T, false>, P, grid, kDkvSmemBytes, stream,
+                            "tcgen05 dK/dV");
+    if (status) return status;
+  }
+
+  if (shared_bias_grad) {
+    DbParams P{};
+    status = encode_pair(&P.map_q, p, p.q, kTile, "query");
+    if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
+    if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
+    if (!status) status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
+    if (status) return status;
+    P.parts = reinterpret_cast<float*>(base + layout.parts);
+    P.lse = lse;
+    P.delta = delta;
+    P.mask = p.mask;
+    P.m_sb = p.mask_sb;
+    P.m_sr = p.mask_sr;
+    P.m_sc = p.mask_sc;
+    P.batch = p.batch;
+    P.rows = p.rows;
+    P.cols = p.cols;
+    P.heads = p.heads;
+    P.tiles = (int)ceil_div(p.cols, kTile);
+    P.num_parts = bias_parts(p);
+    P.rows_per_part = (int)ceil_div(p.rows, P.num_parts);
+    P.scale = p.scale;
+    const unsigned grid = (unsigned)(int64_t(P.num_parts) * p.batch * p.heads * P.tiles * P.tiles);
+    auto kernel = ta_bwd_dbias_kernel<T>;
+    status = reserve_smem(kernel, kDbSmemBytes);
+    if (status) return status;
+    kernel<<<grid, kThreads, kDbSmemBytes, stream>>>(P);
+    count_launch();
+    status = check_launch("tcgen05 shared-bias gradient");
+    if (status) return status;
+    const int64_t plane = int64_t(p.batch) * p.heads * p.cols * p.cols;
+    reduce_parts_kernel<T><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(P.parts, P.num_parts, g.dbias, g.dbias_sb,
+                                                                               g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch,
+                                                                               p.heads, p.cols);
+    count_launch();
+    status = check_launch("tcgen05 shared-bias reduce");
+    if (status) return status;
+  }
+  (void)map_q128;
+  (void)map_d128;
+  (void)map_k128;
+  (void)map_v128;
+  return OOPS_TA_OK;
+}
+
+}  // namespace
+
+bool tensor_backward_applies(const oops_ta_problem& p, const oops_ta_grads* g) {
+  if (!tensor_forward_applies(p)) return false;
+  const int64_t rows = int64_t(p.batch) * p.rows * p.heads * p.cols;
+  if (rows > 0x7fffffffll * 64) return false;
+  (void)g;
+  return true;
+}
+
+uint64_t tensor_backward_workspace(const oops_ta_problem& p, const oops_ta_grads& g) { return workspace_layout(p, g).total; }
+
+int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
+                    const oops_ta_grads& g, cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(dout.ptr) & 15) != 0 || !stride_ok(dout.sb, p.batch) || !stride_ok(dout.sr, p.rows) ||
+      !stride_ok(dout.sc, p.cols) || !stride_ok(dout.sh, p.heads))
+    return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "upstream gradient must be 16-byte aligned with strides that are multiples of 8");
+  if (p.dtype == OOPS_TA_BF16) return run_backward<__nv_bfloat16>(p, out, dout, lse, g, stream);
+  return run_backward<__half>(p, out, dout, lse, g, stream);
+}
+
+int backward_device_status(int reset) { return read_tu_device_status(reset); }
+
+}  // namespace oops_ta

@@ -7,30 +7,17 @@
 // memory, V from shared memory); two softmax warpgroups, one per query tile, read S from tensor
 // memory, add the bias, apply the key mask, run the online softmax in base 2 and write P (packed
 // 16-bit) over S.  While one warpgroup is in its softmax the tensor core works on the other tile.
-#include <cuda.h>
-#include <cuda_runtime.h>
-
-#include <mutex>
-
-#include "sm100_ptx.cuh"
-#include "ta_internal.h"
+#include "ta_tensor_common.cuh"
 
 namespace oops_ta {
-
-__device__ int g_device_status = 0;  // first device-side failure since the last reset (oops_ta_status value)
-
 namespace {
 
 using namespace ptx;
 
-constexpr int kHeadDim = 32;
-constexpr int kTile = 128;         // queries per tile, keys per tile
 constexpr int kStages = 3;         // K/V ring depth
 constexpr int kTileBytes = kTile * kHeadDim * 2;       // 8 KiB: one Q, K or V tile
 constexpr int kBiasBytes = kTile * kTile * 2;          // 32 KiB: one bias tile (two 64-key boxes)
 constexpr int kFwdThreads = 320;   // 2 softmax warpgroups + producer warp + MMA warp
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
 
 struct FwdSmem {
   static constexpr int q = 0;
@@ -373,80 +360,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_con
     }
   }
 
-  // ---------------------------------------------------------------------- teardown
-  tc_fence_before_sync();
-  __syncthreads();
-  if (*abort_flag != 0) {
-    // let copies that are still in flight land before the shared memory goes away
-    const uint64_t start = globaltimer_ns();
-    while (globaltimer_ns() - start < 200000ull) __nanosleep(1000);
-    if (tid == 0) atomicCAS(&g_device_status, 0, (int)OOPS_TA_DEVICE_TIMEOUT);
-    __syncthreads();
-  }
-  if (warp == 9) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// host side
-// ---------------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult query;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query) == cudaSuccess &&
-        query == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
-// 5-D map over (inner, d1, d2, d3, d4); strides in elements for d1..d4 (inner stride is 1).
-int encode_map(CUtensorMap* map, int dtype, const void* ptr, const uint64_t dims[5], const int64_t strides[4],
-               const uint32_t box[5], CUtensorMapSwizzle swizzle, const char* what) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(OOPS_TA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t gdim[5], gstride[4];
-  cuuint32_t gbox[5], estride[5] = {1, 1, 1, 1, 1};
-  uint64_t fallback = dims[0] * 2;
-  for (int i = 0; i < 5; ++i) {
-    gdim[i] = dims[i];
-    gbox[i] = box[i];
-  }
-  for (int i = 0; i < 4; ++i) {
-    uint64_t bytes = uint64_t(strides[i]) * 2;
-    if (dims[i + 1] == 1 && (strides[i] <= 0 || bytes % 16 != 0)) bytes = (fallback + 15) & ~uint64_t(15);
-    gstride[i] = bytes;
-    fallback = bytes * dims[i + 1];
-  }
-  const CUtensorMapDataType type = dtype == OOPS_TA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult rc = fn(map, type, 5, const_cast<void*>(ptr), gdim, gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "tensor map for %s rejected (CUresult %d)", what, (int)rc);
-  return OOPS_TA_OK;
-}
-
-bool stride_ok(int64_t stride, int size) { return size == 1 || (stride > 0 && stride % 8 == 0); }
-
-bool pair_ok(const oops_ta_pair& t, const oops_ta_problem& p) {
-  return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && stride_ok(t.sb, p.batch) && stride_ok(t.sr, p.rows) &&
-         stride_ok(t.sc, p.cols) && stride_ok(t.sh, p.heads);
-}
-
-int encode_pair(CUtensorMap* map, const oops_ta_problem& p, const oops_ta_pair& t, const char* what) {
-  const uint64_t dims[5] = {uint64_t(p.head_dim), uint64_t(p.heads), uint64_t(p.cols), uint64_t(p.rows), uint64_t(p.batch)};
-  const int64_t strides[4] = {t.sh, t.sc, t.sr, t.sb};
-  const uint32_t box[5] = {kHeadDim, 1, kTile, 1, 1};
-  return encode_map(map, p.dtype, t.ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B, what);
+  teardown(abort_flag, tmem_base, 9);
 }
 
 }  // namespace
@@ -467,24 +381,17 @@ bool tensor_forward_applies(const oops_ta_problem& p) {
   return ctas <= 0x7fffffffll;
 }
 
-bool tensor_backward_applies(const oops_ta_problem&, const oops_ta_grads*) { return false; }
-
 uint64_t tensor_forward_workspace(const oops_ta_problem&) { return 0; }
-uint64_t tensor_backward_workspace(const oops_ta_problem&, const oops_ta_grads&) { return 0; }
 
 int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
   FwdParams P{};
-  int status = encode_pair(&P.map_q, p, p.q, "query");
-  if (!status) status = encode_pair(&P.map_k, p, p.k, "key");
-  if (!status) status = encode_pair(&P.map_v, p, p.v, "value");
+  int status = encode_pair(&P.map_q, p, p.q, kTile, "query");
+  if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
+  if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
   if (status) return status;
   const bool has_bias = p.bias_groups != 0;
   if (has_bias) {
-    const uint64_t dims[5] = {uint64_t(p.cols), uint64_t(p.cols), uint64_t(p.heads), uint64_t(p.bias_groups),
-                              uint64_t(p.batch)};
-    const int64_t strides[4] = {p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb};
-    const uint32_t box[5] = {64, kTile, 1, 1, 1};
-    status = encode_map(&P.map_bias, p.dtype, p.bias, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "bias");
+    status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
     if (status) return status;
   }
   P.out = out.ptr;
@@ -512,8 +419,8 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
   auto launch = [&](auto kernel) -> int {
     static thread_local const void* configured = nullptr;
     if (configured != reinterpret_cast<const void*>(kernel)) {
-      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmemBytes) != cudaSuccess)
-        return fail(OOPS_TA_CUDA_ERROR, "cannot reserve %d bytes of shared memory", kFwdSmemBytes);
+      const int rc = reserve_smem(kernel, kFwdSmemBytes);
+      if (rc) return rc;
       configured = reinterpret_cast<const void*>(kernel);
     }
     kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(P);
@@ -525,20 +432,6 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
   return has_bias ? launch(ta_fwd_kernel<__half, true>) : launch(ta_fwd_kernel<__half, false>);
 }
 
-int tensor_backward(const oops_ta_problem&, const oops_ta_pair&, const oops_ta_pair&, const float*, const oops_ta_grads&,
-                    cudaStream_t) {
-  return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "no tcgen05 reverse pass for this problem");
-}
-
-int device_status(int reset) {
-  int value = 0;
-  if (cudaMemcpyFromSymbol(&value, g_device_status, sizeof(int)) != cudaSuccess)
-    return fail(OOPS_TA_CUDA_ERROR, "cannot read the device status word");
-  if (reset && value != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-  }
-  return value;
-}
+int forward_device_status(int reset) { return read_tu_device_status(reset); }
 
 }  // namespace oops_ta
