@@ -33,8 +33,26 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One arrival per warp: every lane has finished its part (the caller has run the fences it needs), lane 0 arrives.
+// Barriers that warps arrive on are initialised with the number of warps, not threads.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
+#ifdef TA_SPIN_TEST_WAIT
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+#endif
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -49,9 +67,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any thread of the CTA has given up, the
 // others stop waiting too.  Returns false if the wait was abandoned.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint64_t kWaitLimitNs = 250000000ull;  // 0.25 s
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef TA_PROFILE_WAITS
+#define TA_WAIT_SLOT(name) unsigned long long name = 0
+#define TA_WAIT_ARG(name) , &name
+#else
+#define TA_WAIT_SLOT(name)
+#define TA_WAIT_ARG(name)
+#endif
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long* waited = nullptr) {
+#ifdef TA_PROFILE_WAITS
+  const long long t0 = clock64();
+  struct Stop {
+    unsigned long long* w;
+    long long t0;
+    __device__ ~Stop() {
+      if (w) *w += (unsigned long long)(clock64() - t0);
+    }
+  } stop{waited, t0};
+#endif
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t start = globaltimer_ns();
   uint32_t spins = 0;
@@ -201,6 +238,38 @@ __device__ __forceinline__ float lg2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Packed pairs of f32 in one 64-bit register (Blackwell issues these as one instruction per pair).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <typename T>
 struct Half2;
 template <>
@@ -213,6 +282,7 @@ struct Half2<__nv_bfloat16> {
   }
   __device__ static __forceinline__ float lo(uint32_t v) { return __uint_as_float(v << 16); }
   __device__ static __forceinline__ float hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+  __device__ static __forceinline__ f32x2 widen(uint32_t v) { return pack2(lo(v), hi(v)); }
 };
 template <>
 struct Half2<__half> {
@@ -226,6 +296,7 @@ struct Half2<__half> {
     return __half2float(__ushort_as_half((unsigned short)(v & 0xffffu)));
   }
   __device__ static __forceinline__ float hi(uint32_t v) { return __half2float(__ushort_as_half((unsigned short)(v >> 16))); }
+  __device__ static __forceinline__ f32x2 widen(uint32_t v) { return pack2(lo(v), hi(v)); }
 };
 
 }  // namespace ptx

@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   auto bar = [&](int index) -> uint32_t { return smem_base + DqSmem::bars + index * 8; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (device_failed()) return;
   int idx = blockIdx.x;
   const int qp = idx % P.q_pairs;
   idx /= P.q_pairs;
@@ -195,17 +196,17 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DqSmem::qd_full + i), 1);
       mbar_init(bar(DqSmem::sd_full + i), 1);
-      mbar_init(bar(DqSmem::ds_full + i), kTile);
+      mbar_init(bar(DqSmem::ds_full + i), kTile / 32);
       mbar_init(bar(DqSmem::dq_done + i), 1);
     }
     for (int i = 0; i < kRing; ++i) {
       mbar_init(bar(DqSmem::kv_full + i), 1);
       mbar_init(bar(DqSmem::kv_empty + i), 1);
-      mbar_init(bar(DqSmem::k_ready + i), kTile);
+      mbar_init(bar(DqSmem::k_ready + i), kTile / 32);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(DqSmem::bias_full + i), 1);
-      mbar_init(bar(DqSmem::bias_empty + i), kTile);
+      mbar_init(bar(DqSmem::bias_empty + i), kTile / 32);
     }
     fence_barrier_init();
   }
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
           row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
-        mbar_arrive(bar(DqSmem::k_ready + st));
+        mbar_arrive_warp(bar(DqSmem::k_ready + st));
       }
       ok = mbar_wait(bar(DqSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
@@ -394,11 +395,11 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
           }
         }
       }
-      if (HAS_BIAS) mbar_arrive(bar(DqSmem::bias_empty + slot));
+      if (HAS_BIAS) mbar_arrive_warp(bar(DqSmem::bias_empty + slot));
       tmem_st32(s_t, packed);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar(DqSmem::ds_full + w));
+      mbar_arrive_warp(bar(DqSmem::ds_full + w));
     }
 
     if (ok) ok = mbar_wait(bar(DqSmem::dq_done + w), 0, abort_flag);
@@ -465,6 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
   auto bar = [&](int index) -> uint32_t { return smem_base + DkvSmem::bars + index * 8; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (device_failed()) return;
   int idx = blockIdx.x;
   const int kp = idx % P.k_pairs;
   idx /= P.k_pairs;
@@ -482,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DkvSmem::kv_full + i), 1);
       mbar_init(bar(DkvSmem::sd_full + i), 1);
-      mbar_init(bar(DkvSmem::pds_full + i), kTile);
+      mbar_init(bar(DkvSmem::pds_full + i), kTile / 32);
       mbar_init(bar(DkvSmem::done + i), 1);
     }
     for (int i = 0; i < kRing; ++i) {
@@ -491,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(DkvSmem::bias_full + i), 1);
-      mbar_init(bar(DkvSmem::bias_empty + i), kTile);
+      mbar_init(bar(DkvSmem::bias_empty + i), kTile / 32);
     }
     fence_barrier_init();
   }
@@ -656,12 +658,12 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
           }
         }
       }
-      if (HAS_BIAS) mbar_arrive(bar(DkvSmem::bias_empty + slot));
+      if (HAS_BIAS) mbar_arrive_warp(bar(DkvSmem::bias_empty + slot));
       tmem_st32(st_t, p_packed);
       tmem_st32(dpt_t, ds_packed);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar(DkvSmem::pds_full + w));
+      mbar_arrive_warp(bar(DkvSmem::pds_full + w));
     }
 
     if (ok) ok = mbar_wait(bar(DkvSmem::done + w), 0, abort_flag);
@@ -732,6 +734,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
   auto bar = [&](int index) -> uint32_t { return smem_base + DbSmem::bars + index * 8; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (device_failed()) return;
   int idx = blockIdx.x;
   const int kt = idx % P.tiles;
   idx /= P.tiles;
@@ -755,7 +758,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DbSmem::sd_full + i), 1);
-      mbar_init(bar(DbSmem::sd_free + i), 2 * kTile);
+      mbar_init(bar(DbSmem::sd_free + i), 2 * kTile / 32);
     }
     fence_barrier_init();
   }
@@ -871,7 +874,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(bar(DbSmem::sd_free + buf));
+      mbar_arrive_warp(bar(DbSmem::sd_free + buf));
     }
     if (ok && q_valid) {
       float* dst = P.parts + (((int64_t(part) * P.batch + b) * P.heads + h) * P.cols + q_index) * P.cols + key_base;

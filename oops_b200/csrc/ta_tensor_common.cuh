@@ -31,9 +31,14 @@ int read_tu_device_status(int reset) {
   return value;
 }
 
+// After a kernel has given up a wait, the kernels of this translation unit return at once until the host
+// clears the word (oops_ta_device_status(1)): one stuck wait must not be repeated by every later CTA.
+__device__ __forceinline__ bool device_failed() { return *reinterpret_cast<volatile int*>(&g_tu_device_status) != 0; }
+
 // Shared tail of every tcgen05 kernel: after the CTA-wide barrier, a CTA that abandoned a wait lets
 // its in-flight copies land and records the failure; then the allocating warp frees tensor memory.
-__device__ __forceinline__ void teardown(volatile int* abort_flag, uint32_t tmem_base, int alloc_warp) {
+__device__ __forceinline__ void teardown(volatile int* abort_flag, uint32_t tmem_base, int alloc_warp,
+                                         uint32_t tmem_cols = 512) {
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0) {
@@ -44,7 +49,7 @@ __device__ __forceinline__ void teardown(volatile int* abort_flag, uint32_t tmem
   }
   if ((int)(threadIdx.x >> 5) == alloc_warp) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, 512);
+    ptx::tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 

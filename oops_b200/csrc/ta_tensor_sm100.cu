@@ -14,35 +14,58 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kStages = 3;         // K/V ring depth
-constexpr int kTileBytes = kTile * kHeadDim * 2;       // 8 KiB: one Q, K or V tile
-constexpr int kBiasBytes = kTile * kTile * 2;          // 32 KiB: one bias tile (two 64-key boxes)
-constexpr int kFwdThreads = 320;   // 2 softmax warpgroups + producer warp + MMA warp
+#ifdef TA_PROFILE_WAITS
+// clocks spent waiting, summed over CTAs: 0 s_full, 1 bias_full, 2 v_full(wg0), 3 o_final, 4 mma:p_full, 5 mma:k_full,
+// 6 mma:v, 7 producer:k_empty, 8 producer:v_empty, 9 producer:bias_empty, 10 softmax loop clocks (thread 0), 11 CTA count
+__device__ unsigned long long g_wait_clk[32];
+#define TA_ADD(slot, value) atomicAdd(&g_wait_clk[slot], (unsigned long long)(value))
+#else
+#define TA_ADD(slot, value)
+#endif
+
+constexpr int kStages = 3;                       // K/V ring depth
+constexpr int kKeys = 64;                        // keys per step
+constexpr int kQBytes = kTile * kHeadDim * 2;    // 8 KiB: one 128-query Q tile
+constexpr int kKvBytes = kKeys * kHeadDim * 2;   // 4 KiB: one K or V step
+constexpr int kBiasBytes = kTile * kKeys * 2;    // 16 KiB: one 128 x 64 bias tile (one swizzle-128 box)
+constexpr int kFwdThreads = 320;                 // 2 softmax warpgroups + producer warp + MMA warp
+constexpr int kFwdTmemCols = 256;                // S 2x64 | P 2x32 | O 2x32; two CTAs share an SM
+constexpr int kMaxKeepWords = 512;               // keep-bit table: one bit per key column, cols <= 16384
 
 struct FwdSmem {
-  static constexpr int q = 0;
-  static constexpr int k = q + 2 * kTileBytes;
-  static constexpr int v = k + kStages * kTileBytes;
-  static constexpr int bias = v + kStages * kTileBytes;
+  static constexpr int q = 0;                          // [2]
+  static constexpr int k = q + 2 * kQBytes;            // [kStages]
+  static constexpr int v = k + kStages * kKvBytes;     // [kStages]
+  static constexpr int bias = v + kStages * kKvBytes;  // [2 tiles][2 buffers]
   static constexpr int bars = bias + 4 * kBiasBytes;
   // barrier indices (8 bytes each)
-  static constexpr int q_full = 0;                   // [2]
-  static constexpr int k_full = q_full + 2;          // [kStages]
-  static constexpr int k_empty = k_full + kStages;   // [kStages]
-  static constexpr int v_full = k_empty + kStages;   // [kStages]
-  static constexpr int v_empty = v_full + kStages;   // [kStages]
-  static constexpr int v_ready = v_empty + kStages;  // [kStages]
+  static constexpr int q_full = 0;                     // [2]
+  static constexpr int k_full = q_full + 2;            // [kStages]
+  static constexpr int k_empty = k_full + kStages;     // [kStages]
+  static constexpr int v_full = k_empty + kStages;     // [kStages]
+  static constexpr int v_empty = v_full + kStages;     // [kStages]
+  static constexpr int v_ready = v_empty + kStages;    // [kStages]
   static constexpr int bias_full = v_ready + kStages;  // [2 tiles][2 buffers]
   static constexpr int bias_empty = bias_full + 4;     // [2][2]
   static constexpr int s_full = bias_empty + 4;        // [2]
   static constexpr int p_full = s_full + 2;            // [2]
-  static constexpr int o_done = p_full + 2;            // [2]
-  static constexpr int num_bars = o_done + 2;
+  static constexpr int o_final = p_full + 2;           // [2]
+  static constexpr int s_free = o_final + 2;           // [2] S has been read into registers
+  static constexpr int pv_done = s_free + 2;           // [2] the latest P V product has completed
+  static constexpr int num_bars = pv_done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
-  static constexpr int total = abort_flag + 4;
+  static constexpr int keep = abort_flag + 4;          // [kMaxKeepWords] u32
+  static constexpr int total = keep + kMaxKeepWords * 4;
 };
+#ifdef TA_EXP_ONE_CTA
+constexpr int kFwdSmemBytes = FwdSmem::total + 1024 + 8192;
+#else
 constexpr int kFwdSmemBytes = FwdSmem::total + 1024;  // slack to align the base to 1 KiB
+#endif
+#ifndef TA_EXP_ONE_CTA
+static_assert(kFwdSmemBytes <= 113 * 1024, "two forward CTAs must fit in one SM's shared memory");
+#endif
 
 struct FwdParams {
   CUtensorMap map_q, map_k, map_v, map_bias;
@@ -52,23 +75,30 @@ struct FwdParams {
   const uint8_t* mask;
   int64_t m_sb, m_sr, m_sc;
   int batch, rows, cols, heads, bias_groups;
-  int q_pairs, k_tiles;
+  int q_pairs, k_steps;
   int out_vec16;
   float scale;
 };
 
+// The running maximum is only raised when a step exceeds it by more than this (natural-log units):
+// probabilities then stay below e^kRescaleSlack, far inside the f32 / 16-bit ranges, and the
+// accumulator rescale (a tensor-memory round trip) is skipped for almost every step.
+constexpr float kRescaleSlack = 5.545177444f;  // 8 * ln 2
+
 template <typename T, bool HAS_BIAS>
-__global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_constant__ FwdParams P) {
+__global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_constant__ FwdParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + FwdSmem::abort_flag);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + FwdSmem::tmem_slot);
+  uint32_t* keep_words = reinterpret_cast<uint32_t*>(smem_gen + FwdSmem::keep);
   auto bar = [&](int index) -> uint32_t { return smem_base + FwdSmem::bars + index * 8; };
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  if (device_failed()) return;
 
   // work decomposition: query pair fastest, then head, row, batch
   int idx = blockIdx.x;
@@ -80,9 +110,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_con
   const int b = idx / P.rows;
   const int q0 = qp * 2 * kTile;
   const int n_tiles = (q0 + kTile < P.cols) ? 2 : 1;
-  const int KT = P.k_tiles;
+  const int KS = P.k_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   const bool has_mask = P.mask != nullptr;
+  // Steps need keep-bits when there is a mask or when the last key step is ragged.
+  const bool has_bits = has_mask || (P.cols % kKeys) != 0;
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -92,215 +124,296 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_con
       mbar_init(bar(FwdSmem::k_empty + i), 1);
       mbar_init(bar(FwdSmem::v_full + i), 1);
       mbar_init(bar(FwdSmem::v_empty + i), 1);
-      mbar_init(bar(FwdSmem::v_ready + i), kTile);
+      mbar_init(bar(FwdSmem::v_ready + i), kTile / 32);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(FwdSmem::bias_full + i), 1);
-      mbar_init(bar(FwdSmem::bias_empty + i), kTile);
+      mbar_init(bar(FwdSmem::bias_empty + i), kTile / 32);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(FwdSmem::s_full + i), 1);
-      mbar_init(bar(FwdSmem::p_full + i), kTile);
-      mbar_init(bar(FwdSmem::o_done + i), 1);
+      mbar_init(bar(FwdSmem::p_full + i), kTile / 32);
+      mbar_init(bar(FwdSmem::o_final + i), 1);
+      mbar_init(bar(FwdSmem::s_free + i), kTile / 32);
+      mbar_init(bar(FwdSmem::pv_done + i), 1);
     }
     fence_barrier_init();
   }
   if (warp == 9) {
-    tmem_alloc(smem_base + FwdSmem::tmem_slot, 512);
+    tmem_alloc(smem_base + FwdSmem::tmem_slot, kFwdTmemCols);
     tmem_relinquish();
     tc_fence_before_sync();
+  }
+  if (has_bits && warp < 8) {
+    // one bit per key of this pair row: kept by the mask and inside the row
+    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+    for (int word = warp; word < KS * 2; word += 8) {
+      const int key = word * 32 + lane;
+      bool keep = key < P.cols;
+      if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+      const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) keep_words[word] = bits;
+    }
   }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // tensor-memory columns
+  constexpr int kSCol = 0, kPCol = 2 * kKeys, kOCol = 2 * kKeys + 2 * (kKeys / 2);
 
   if (warp == 8) {
     // ------------------------------------------------------------------ producer (one thread)
     if (lane == 0) {
       bool ok = true;
+      TA_WAIT_SLOT(wk); TA_WAIT_SLOT(wv); TA_WAIT_SLOT(wb);
       for (int w = 0; w < n_tiles; ++w) {
-        mbar_expect_tx(bar(FwdSmem::q_full + w), kTileBytes);
-        tma_load_5d(smem_base + FwdSmem::q + w * kTileBytes, &P.map_q, bar(FwdSmem::q_full + w), 0, h, q0 + w * kTile, r, b);
+        mbar_expect_tx(bar(FwdSmem::q_full + w), kQBytes);
+        tma_load_5d(smem_base + FwdSmem::q + w * kQBytes, &P.map_q, bar(FwdSmem::q_full + w), 0, h, q0 + w * kTile, r, b);
       }
-      for (int j = 0; j < KT && ok; ++j) {
+      for (int j = 0; j < KS && ok; ++j) {
         const int st = j % kStages, round = j / kStages;
-        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::k_empty + st), (round - 1) & 1, abort_flag);
+        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::k_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wk));
         if (!ok) break;
-        mbar_expect_tx(bar(FwdSmem::k_full + st), kTileBytes);
-        tma_load_5d(smem_base + FwdSmem::k + st * kTileBytes, &P.map_k, bar(FwdSmem::k_full + st), 0, h, j * kTile, r, b);
-        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::v_empty + st), (round - 1) & 1, abort_flag);
-        if (!ok) break;
-        mbar_expect_tx(bar(FwdSmem::v_full + st), kTileBytes);
-        tma_load_5d(smem_base + FwdSmem::v + st * kTileBytes, &P.map_v, bar(FwdSmem::v_full + st), 0, h, j * kTile, r, b);
+        mbar_expect_tx(bar(FwdSmem::k_full + st), kKvBytes);
+        tma_load_5d(smem_base + FwdSmem::k + st * kKvBytes, &P.map_k, bar(FwdSmem::k_full + st), 0, h, j * kKeys, r, b);
         if (HAS_BIAS) {
           const int buf = j & 1;
           for (int w = 0; w < n_tiles && ok; ++w) {
             const int slot = w * 2 + buf;
-            if (j >= 2) ok = mbar_wait(bar(FwdSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
+            if (j >= 2) ok = mbar_wait(bar(FwdSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag TA_WAIT_ARG(wb));
             if (!ok) break;
             mbar_expect_tx(bar(FwdSmem::bias_full + slot), kBiasBytes);
-            const uint32_t dst = smem_base + FwdSmem::bias + slot * kBiasBytes;
-            tma_load_5d(dst, &P.map_bias, bar(FwdSmem::bias_full + slot), j * kTile, q0 + w * kTile, h, g, b);
-            tma_load_5d(dst + kBiasBytes / 2, &P.map_bias, bar(FwdSmem::bias_full + slot), j * kTile + 64,
-                        q0 + w * kTile, h, g, b);
+            tma_load_5d(smem_base + FwdSmem::bias + slot * kBiasBytes, &P.map_bias, bar(FwdSmem::bias_full + slot),
+                        j * kKeys, q0 + w * kTile, h, g, b);
           }
         }
+        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::v_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wv));
+        if (!ok) break;
+        mbar_expect_tx(bar(FwdSmem::v_full + st), kKvBytes);
+        tma_load_5d(smem_base + FwdSmem::v + st * kKvBytes, &P.map_v, bar(FwdSmem::v_full + st), 0, h, j * kKeys, r, b);
       }
+      TA_ADD(7, wk); TA_ADD(8, wv); TA_ADD(9, wb);
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
-      constexpr uint32_t idesc_qk = instr_desc(fmt, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_qk = instr_desc(fmt, 0, 0, kTile, kKeys);
       constexpr uint32_t idesc_pv = instr_desc(fmt, 0, 1, kTile, kHeadDim);
-      const uint32_t v_ready_base = has_mask ? FwdSmem::v_ready : FwdSmem::v_full;
       bool ok = true;
+      TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wk); TA_WAIT_SLOT(wv);
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(FwdSmem::q_full + w), 0, abort_flag);
-      for (int j = 0; j <= KT && ok; ++j) {
-        if (j < KT) ok = mbar_wait(bar(FwdSmem::k_full + j % kStages), (j / kStages) & 1, abort_flag);
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          const uint32_t s_tmem = tmem_base + w * kTile;
-          const uint32_t o_tmem = tmem_base + 2 * kTile + w * kHeadDim;
-          if (j > 0) {
-            const int jj = j - 1, st = jj % kStages;
-            ok = mbar_wait(bar(FwdSmem::p_full + w), jj & 1, abort_flag);
-            if (ok && w == 0) ok = mbar_wait(bar(v_ready_base + st), (jj / kStages) & 1, abort_flag);
+      // S[128 x 64] = Q[128 x 32] K[64 x 32]^T; both K-major, 64-byte swizzle: 8-row groups 512 bytes apart,
+      // each 16-channel step advances 32 bytes inside the swizzle span.
+      auto issue_qk = [&](int j, int w) {
+        const int st = j % kStages;
+        const uint64_t qdesc = smem_desc(smem_base + FwdSmem::q + w * kQBytes, 16, 512, kSwizzle64B);
+        const uint64_t kdesc = smem_desc(smem_base + FwdSmem::k + st * kKvBytes, 16, 512, kSwizzle64B);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(tmem_base + kSCol + w * kKeys, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
+        mma_commit(bar(FwdSmem::s_full + w));
+        if (w == n_tiles - 1) mma_commit(bar(FwdSmem::k_empty + st));
+      };
+      if (ok) ok = mbar_wait(bar(FwdSmem::k_full), 0, abort_flag TA_WAIT_ARG(wk));
+      if (ok) {
+        tc_fence_after_sync();
+        for (int w = 0; w < n_tiles; ++w) issue_qk(0, w);
+      }
+      for (int j = 0; j < KS && ok; ++j) {
+        if (j + 1 < KS) {
+          // next score tiles: issued as soon as a warpgroup has pulled S(j) into registers, so that S(j+1) is
+          // ready when its softmax of step j ends (P has its own tensor-memory columns)
+          ok = mbar_wait(bar(FwdSmem::k_full + (j + 1) % kStages), ((j + 1) / kStages) & 1, abort_flag TA_WAIT_ARG(wk));
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(FwdSmem::s_free + w), j & 1, abort_flag TA_WAIT_ARG(wp));
             if (!ok) break;
             tc_fence_after_sync();
-            // O[128 x 32] += P[128 x 128] V[128 x 32]; V is MN-major (channel contiguous), 64-byte swizzle:
-            // 8-key groups are 512 bytes apart, each 16-key step advances 1024 bytes.
-            const uint64_t vdesc = smem_desc(smem_base + FwdSmem::v + st * kTileBytes, 16, 512, kSwizzle64B);
-#pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk)
-              mma_ts(o_tmem, s_tmem + kk * 8, vdesc + uint64_t(kk * (1024 >> 4)), idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
-            mma_commit(bar(FwdSmem::o_done + w));
-            if (w == n_tiles - 1) mma_commit(bar(FwdSmem::v_empty + st));
-          }
-          if (j < KT) {
-            const int st = j % kStages;
-            tc_fence_after_sync();
-            // S[128 x 128] = Q[128 x 32] K[128 x 32]^T; both K-major, 64-byte swizzle: 8-row groups 512 bytes apart,
-            // each 16-channel step advances 32 bytes inside the swizzle span.
-            const uint64_t qdesc = smem_desc(smem_base + FwdSmem::q + w * kTileBytes, 16, 512, kSwizzle64B);
-            const uint64_t kdesc = smem_desc(smem_base + FwdSmem::k + st * kTileBytes, 16, 512, kSwizzle64B);
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)
-              mma_ss(s_tmem, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc_qk, kk > 0 ? 1u : 0u);
-            mma_commit(bar(FwdSmem::s_full + w));
-            if (w == n_tiles - 1) mma_commit(bar(FwdSmem::k_empty + st));
+            issue_qk(j + 1, w);
           }
         }
+        const int st = j % kStages;
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          ok = mbar_wait(bar(FwdSmem::p_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+          if (ok && w == 0) {
+            ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
+            // with a mask, warpgroup 0 signs off every value step after clearing the rows of dropped keys
+            if (ok && has_mask) ok = mbar_wait(bar(FwdSmem::v_ready + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
+          }
+          if (!ok) break;
+          tc_fence_after_sync();
+          // O[128 x 32] += P[128 x 64] V[64 x 32]; V is MN-major (channel contiguous), 64-byte swizzle:
+          // 8-key groups are 512 bytes apart, each 16-key step advances 1024 bytes.
+          const uint32_t p_tmem = tmem_base + kPCol + w * (kKeys / 2);
+          const uint32_t o_tmem = tmem_base + kOCol + w * kHeadDim;
+          const uint64_t vdesc = smem_desc(smem_base + FwdSmem::v + st * kKvBytes, 16, 512, kSwizzle64B);
+#pragma unroll
+          for (int kk = 0; kk < kKeys / 16; ++kk)
+            mma_ts(o_tmem, p_tmem + kk * 8, vdesc + uint64_t(kk * (1024 >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(bar(FwdSmem::pv_done + w));
+          if (j == KS - 1) mma_commit(bar(FwdSmem::o_final + w));
+          if (w == n_tiles - 1) mma_commit(bar(FwdSmem::v_empty + st));
+        }
       }
+      TA_ADD(4, wp); TA_ADD(5, wk); TA_ADD(6, wv);
     }
   } else if ((warp >> 2) < n_tiles) {
     // ------------------------------------------------------------------ softmax warpgroups
     const int w = warp >> 2;
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_field + w * kTile;
-    const uint32_t o_tmem = tmem_base + lane_field + 2 * kTile + w * kHeadDim;
+    const uint32_t s_tmem = tmem_base + lane_field + kSCol + w * kKeys;
+    const uint32_t p_tmem = tmem_base + lane_field + kPCol + w * (kKeys / 2);
+    const uint32_t o_tmem = tmem_base + lane_field + kOCol + w * kHeadDim;
     const int q_index = q0 + w * kTile + t;
-    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
-    const float scale = P.scale;
+    const f32x2 scale2 = pack2(P.scale, P.scale);
+    const f32x2 log2e2 = pack2(kLog2e, kLog2e);
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    TA_WAIT_SLOT(ws); TA_WAIT_SLOT(wbias); TA_WAIT_SLOT(wvf); TA_WAIT_SLOT(wo);
+#ifdef TA_PROFILE_WAITS
+    const long long loop_start = clock64();
+#endif
 
-    for (int j = 0; j < KT && ok; ++j) {
-      // keep-bits of this key tile (all threads of a warp hold all four words)
-      uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      const bool need_bits = has_mask || (j == KT - 1 && (P.cols % kTile) != 0);
-      if (need_bits) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int key = j * kTile + i * 32 + lane;
-          bool keep = key < P.cols;
-          if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
-          bits[i] = __ballot_sync(0xffffffffu, keep);
-        }
+    for (int j = 0; j < KS && ok; ++j) {
+      uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
+      bool all_kept = true;
+      if (has_bits) {
+        const uint2 wds = *reinterpret_cast<const uint2*>(keep_words + j * 2);
+        bits[0] = wds.x; bits[1] = wds.y;
+        all_kept = (wds.x & wds.y) == 0xffffffffu;
       }
-      const bool all_kept = (bits[0] & bits[1] & bits[2] & bits[3]) == 0xffffffffu;
       if (has_mask && w == 0) {
         // Values of dropped keys must not reach the tensor core (0 * inf): clear their rows in shared memory.
+        // Every step is signed off (one barrier phase per step); only steps with dropped keys are touched.
         const int st = j % kStages;
-        ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag);
-        if (!ok) break;
-        if (!all_kept && ((bits[t >> 5] >> (t & 31)) & 1u) == 0) {
-          uint4* row = reinterpret_cast<uint4*>(smem_gen + FwdSmem::v + st * kTileBytes + t * 64);
-          row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+        if (!all_kept) {
+          ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wvf));
+          if (!ok) break;
+          if (t < kKeys && ((bits[t >> 5] >> (t & 31)) & 1u) == 0) {
+            uint4* row = reinterpret_cast<uint4*>(smem_gen + FwdSmem::v + st * kKvBytes + t * 64);
+            row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
-        mbar_arrive(bar(FwdSmem::v_ready + st));
+        mbar_arrive_warp(bar(FwdSmem::v_ready + st));
       }
 
-      ok = mbar_wait(bar(FwdSmem::s_full + w), j & 1, abort_flag);
+      ok = mbar_wait(bar(FwdSmem::s_full + w), j & 1, abort_flag TA_WAIT_ARG(ws));
       if (!ok) break;
       tc_fence_after_sync();
-      float x[kTile];
+#ifdef TA_PROFILE_WAITS
+      const long long c0 = clock64();
+#endif
+      f32x2 x[kKeys / 2];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kKeys / 32; ++c) {
         uint32_t raw[32];
         tmem_ld32(s_tmem + c * 32, raw);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(raw[i]);
+        for (int i = 0; i < 16; ++i) x[c * 16 + i] = pack2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
       }
       tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(FwdSmem::s_free + w));
+#ifdef TA_PROFILE_WAITS
+      const long long c1 = clock64();
+#endif
 
+#ifdef TA_EXP_SKIP_MATH
+      uint32_t packed[kKeys / 2];
+#pragma unroll
+      for (int i = 0; i < kKeys / 2; ++i) packed[i] = (uint32_t)(x[i] >> 17) & 0x3f003f00u;
+      const bool raise = false;
+      const float alpha = 1.f;
+      l_run = 1.f;
       if (HAS_BIAS) {
         const int slot = w * 2 + (j & 1);
-        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
+        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag TA_WAIT_ARG(wbias));
         if (!ok) break;
-        const uint8_t* tile = smem_gen + FwdSmem::bias + slot * kBiasBytes;
+        mbar_arrive_warp(bar(FwdSmem::bias_empty + slot));
+      }
+#else
+      if (HAS_BIAS) {
+        const int slot = w * 2 + (j & 1);
+        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag TA_WAIT_ARG(wbias));
+        if (!ok) break;
+        const uint8_t* row = smem_gen + FwdSmem::bias + slot * kBiasBytes + t * 128;
+        uint4 bv[8];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint8_t* row = tile + half * (kBiasBytes / 2) + t * 128;
+        for (int c = 0; c < 8; ++c) bv[c] = *reinterpret_cast<const uint4*>(row + ((c ^ (t & 7)) << 4));
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ (t & 7)) << 4));
-            const int at = half * 64 + c * 8;
-            x[at + 0] = fmaf(x[at + 0], scale, Half2<T>::lo(v.x));
-            x[at + 1] = fmaf(x[at + 1], scale, Half2<T>::hi(v.x));
-            x[at + 2] = fmaf(x[at + 2], scale, Half2<T>::lo(v.y));
-            x[at + 3] = fmaf(x[at + 3], scale, Half2<T>::hi(v.y));
-            x[at + 4] = fmaf(x[at + 4], scale, Half2<T>::lo(v.z));
-            x[at + 5] = fmaf(x[at + 5], scale, Half2<T>::hi(v.z));
-            x[at + 6] = fmaf(x[at + 6], scale, Half2<T>::lo(v.w));
-            x[at + 7] = fmaf(x[at + 7], scale, Half2<T>::hi(v.w));
-          }
+        for (int c = 0; c < 8; ++c) {
+          x[c * 4 + 0] = fma2(x[c * 4 + 0], scale2, Half2<T>::widen(bv[c].x));
+          x[c * 4 + 1] = fma2(x[c * 4 + 1], scale2, Half2<T>::widen(bv[c].y));
+          x[c * 4 + 2] = fma2(x[c * 4 + 2], scale2, Half2<T>::widen(bv[c].z));
+          x[c * 4 + 3] = fma2(x[c * 4 + 3], scale2, Half2<T>::widen(bv[c].w));
         }
-        mbar_arrive(bar(FwdSmem::bias_empty + slot));
+        mbar_arrive_warp(bar(FwdSmem::bias_empty + slot));
       } else {
 #pragma unroll
-        for (int i = 0; i < kTile; ++i) x[i] *= scale;
+        for (int i = 0; i < kKeys / 2; ++i) x[i] = mul2(x[i], scale2);
       }
       if (!all_kept) {
 #pragma unroll
-        for (int i = 0; i < kTile; ++i)
-          if (((bits[i >> 5] >> (i & 31)) & 1u) == 0) x[i] = -INFINITY;
+        for (int i = 0; i < kKeys / 2; ++i) {
+          float lo, hi;
+          unpack2(x[i], lo, hi);
+          if (((bits[(2 * i) >> 5] >> ((2 * i) & 31)) & 1u) == 0) lo = -INFINITY;
+          if (((bits[(2 * i + 1) >> 5] >> ((2 * i + 1) & 31)) & 1u) == 0) hi = -INFINITY;
+          x[i] = pack2(lo, hi);
+        }
       }
-      float peak = x[0];
+      float peaks[8];
 #pragma unroll
-      for (int i = 1; i < kTile; ++i) peak = fmaxf(peak, x[i]);
-      const float m_new = fmaxf(m_run, peak);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2((m_run - m_use) * kLog2e);
+      for (int i = 0; i < 8; ++i) {
+        float lo, hi;
+        unpack2(x[i], lo, hi);
+        peaks[i] = fmaxf(lo, hi);
+      }
+#pragma unroll
+      for (int i = 8; i < kKeys / 2; ++i) {
+        float lo, hi;
+        unpack2(x[i], lo, hi);
+        peaks[i & 7] = max3(peaks[i & 7], lo, hi);
+      }
+      const float peak = fmaxf(max3(peaks[0], peaks[1], peaks[2]), max3(max3(peaks[3], peaks[4], peaks[5]), peaks[6], peaks[7]));
+      // raise the running maximum only when it is exceeded by more than the slack (always on the first finite step)
+      const bool raise = peak > m_run + kRescaleSlack || (m_run == -INFINITY && peak > -INFINITY);
+      const float m_old = m_run;
+      if (raise) m_run = peak;
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      const float alpha = raise ? ex2((m_old - m_use) * kLog2e) : 1.f;
       const float shift = -m_use * kLog2e;
-      float total = 0.f;
-      uint32_t packed[kTile / 2];
+      const f32x2 shift2 = pack2(shift, shift);
+      f32x2 totals[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
+      uint32_t packed[kKeys / 2];
 #pragma unroll
-      for (int i = 0; i < kTile; i += 2) {
-        const float p0 = ex2(fmaf(x[i], kLog2e, shift));
-        const float p1 = ex2(fmaf(x[i + 1], kLog2e, shift));
-        total += p0 + p1;
-        packed[i >> 1] = Half2<T>::pack(p0, p1);
+      for (int i = 0; i < kKeys / 2; ++i) {
+        float lo, hi;
+        unpack2(fma2(x[i], log2e2, shift2), lo, hi);
+#ifdef TA_EXP_NOEXP
+        const float p0 = lo, p1 = hi;
+#else
+        const float p0 = ex2(lo), p1 = ex2(hi);
+#endif
+        totals[i & 3] = add2(totals[i & 3], pack2(p0, p1));
+        packed[i] = Half2<T>::pack(p0, p1);
       }
-      l_run = l_run * alpha + total;
-      m_run = m_new;
-
+      float t_lo, t_hi;
+      unpack2(add2(add2(totals[0], totals[1]), add2(totals[2], totals[3])), t_lo, t_hi);
+      l_run = l_run * alpha + (t_lo + t_hi);
+#endif  // TA_EXP_SKIP_MATH
+#ifdef TA_PROFILE_WAITS
+      const long long c2 = clock64();
+#endif
       if (j > 0) {
-        // rescale the running output once the previous P V product has landed
-        ok = mbar_wait(bar(FwdSmem::o_done + w), (j - 1) & 1, abort_flag);
+        // the previous P V product must have finished with O and with the P columns before either is touched
+        ok = mbar_wait(bar(FwdSmem::pv_done + w), (j - 1) & 1, abort_flag TA_WAIT_ARG(wo));
         if (!ok) break;
         tc_fence_after_sync();
+      }
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
         uint32_t acc[32];
         tmem_ld32(o_tmem, acc);
         tmem_wait_ld();
@@ -308,21 +421,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_con
         for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
         tmem_st32(o_tmem, acc);
       }
-      {
-        uint32_t part[32];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) part[i] = packed[c * 32 + i];
-          tmem_st32(s_tmem + c * 32, part);
-        }
-      }
+      tmem_st32(p_tmem, packed);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar(FwdSmem::p_full + w));
+      mbar_arrive_warp(bar(FwdSmem::p_full + w));
+#ifdef TA_PROFILE_WAITS
+      if (t == 0) { const int o = n_tiles == 1 ? 16 : 0; TA_ADD(o + 12, c1 - c0); TA_ADD(o + 13, c2 - c1); TA_ADD(o + 14, clock64() - c2); TA_ADD(o + 15, 1); }
+#endif
     }
 
-    if (ok) ok = mbar_wait(bar(FwdSmem::o_done + w), (KT - 1) & 1, abort_flag);
+#ifdef TA_PROFILE_WAITS
+    if (t == 0) { TA_ADD(10, clock64() - loop_start); TA_ADD(11, 1); }
+#endif
+    if (ok) ok = mbar_wait(bar(FwdSmem::o_final + w), 0, abort_flag TA_WAIT_ARG(wo));
+#ifdef TA_PROFILE_WAITS
+    if (t == 0) { TA_ADD(0, ws); TA_ADD(1, wbias); TA_ADD(2, wvf); TA_ADD(3, wo); }
+#endif
     if (ok) {
       tc_fence_after_sync();
       uint32_t acc[32];
@@ -340,27 +454,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) ta_fwd_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 4; ++i) d4[i] = make_uint4(o2[4 * i], o2[4 * i + 1], o2[4 * i + 2], o2[4 * i + 3]);
         } else {
-          uint32_t* d1 = reinterpret_cast<uint32_t*>(dst);
-          if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+          unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) d1[i] = o2[i];
-          } else {
-            unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              d0[2 * i] = (unsigned short)(o2[i] & 0xffffu);
-              d0[2 * i + 1] = (unsigned short)(o2[i] >> 16);
-            }
+          for (int i = 0; i < 16; ++i) {
+            d0[2 * i] = (unsigned short)(o2[i] & 0xffffu);
+            d0[2 * i + 1] = (unsigned short)(o2[i] >> 16);
           }
         }
-        if (P.lse)
+        if (P.lse) {
+          const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
           P.lse[((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index] =
-              l_run > 0.f ? (m_run + lg2(l_run) * kLn2) : 0.f;
+              l_run > 0.f ? (m_use + lg2(l_run) * kLn2) : 0.f;
+        }
       }
     }
   }
-
-  teardown(abort_flag, tmem_base, 9);
+  teardown(abort_flag, tmem_base, 9, kFwdTmemCols);
 }
 
 }  // namespace
@@ -377,6 +486,7 @@ bool tensor_forward_applies(const oops_ta_problem& p) {
       return false;
     if (p.cols == 1) return false;
   }
+  if (p.cols > kMaxKeepWords * 32) return false;
   const int64_t ctas = int64_t(p.batch) * p.rows * p.heads * ceil_div(p.cols, 2 * kTile);
   return ctas <= 0x7fffffffll;
 }
@@ -386,8 +496,8 @@ uint64_t tensor_forward_workspace(const oops_ta_problem&) { return 0; }
 int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
   FwdParams P{};
   int status = encode_pair(&P.map_q, p, p.q, kTile, "query");
-  if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
-  if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
+  if (!status) status = encode_pair(&P.map_k, p, p.k, kKeys, "key");
+  if (!status) status = encode_pair(&P.map_v, p, p.v, kKeys, "value");
   if (status) return status;
   const bool has_bias = p.bias_groups != 0;
   if (has_bias) {
@@ -412,7 +522,7 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
   P.heads = p.heads;
   P.bias_groups = p.bias_groups;
   P.q_pairs = (int)ceil_div(p.cols, 2 * kTile);
-  P.k_tiles = (int)ceil_div(p.cols, kTile);
+  P.k_steps = (int)ceil_div(p.cols, kKeys);
   P.scale = p.scale;
   const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.q_pairs);
 
@@ -433,5 +543,16 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
 }
 
 int forward_device_status(int reset) { return read_tu_device_status(reset); }
+
+#ifdef TA_PROFILE_WAITS
+extern "C" int oops_ta_debug_wait_clocks(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_wait_clk, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long zero[32] = {0};
+    cudaMemcpyToSymbol(g_wait_clk, zero, sizeof(zero));
+  }
+  return 0;
+}
+#endif
 
 }  // namespace oops_ta
