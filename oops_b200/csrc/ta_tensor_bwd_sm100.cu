@@ -25,7 +25,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 576;
 constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
 constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
 constexpr int kSmallTile = kStep * kHeadDim * 2;        // 4 KiB: 64 x 32 tile
@@ -127,6 +127,70 @@ __device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// shared pieces of the three tensor kernels
+// ---------------------------------------------------------------------------------------------
+// 576 threads: warps 0-15 are four warpgroups of 128 threads that do the element-wise work, warp 16 is
+// the TMA producer, warp 17 issues the MMAs and owns the tensor-memory allocation.  The element-wise
+// work of the reverse pass has no reduction along a score row, so the 64 columns of a step are split
+// between two warpgroups that address the same tensor-memory lanes (warp % 4 selects the lanes).
+
+constexpr int kProducerWarp = 16, kMmaWarp = 17;
+
+#ifdef TA_PROFILE_WAITS
+// dK/dV kernel, clocks summed over warpgroups (thread 0 of each): 0 sd_full, 1 bias_full, 2 pds_done, 3 stats+named barrier,
+// 4 compute, 5 store+arrive, 6 loop total, 7 warpgroup count; MMA thread: 8 sd_free, 9 pds_full, 10 qd_full, 11 loop total,
+// 12 CTA count; producer: 13 qd_empty, 14 bias_empty
+__device__ unsigned long long g_bwd_clk[16];
+#define TB_ADD(slot, value) atomicAdd(&g_bwd_clk[slot], (unsigned long long)(value))
+#define TB_CLOCK(name) const long long name = clock64()
+#else
+#define TB_ADD(slot, value)
+#define TB_CLOCK(name)
+#endif
+constexpr int kMaxKeepWords = 512;  // keep-bit table: one bit per key column, cols <= 16384
+
+// Eight columns of the reverse-pass element math on packed f32 pairs:
+//   p  = 2^(s * (scale*log2e) + bias * log2e + nl)        nl = -lse * log2e
+//   ds = p * (dp + nd)                                     nd = -delta
+// sraw/draw are the tensor-memory words of S and dP (adjacent columns form a pair), bias_chunk points at
+// eight 16-bit bias values, nl2/nd2 hold the four (nl, nl') and (nd, nd') pairs of these columns.
+template <typename T, bool HAS_BIAS>
+__device__ __forceinline__ void score_grad8(const uint32_t* sraw, const uint32_t* draw, const uint8_t* bias_chunk, f32x2 c2,
+                                            f32x2 log2e2, const f32x2* nl2, const f32x2* nd2, f32x2* p2, f32x2* ds2) {
+  uint32_t bw[4] = {0, 0, 0, 0};
+  if (HAS_BIAS) {
+    const uint4 v = *reinterpret_cast<const uint4*>(bias_chunk);
+    bw[0] = v.x; bw[1] = v.y; bw[2] = v.z; bw[3] = v.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const f32x2 s2 = pack2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1]));
+    const f32x2 d2 = pack2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1]));
+    const f32x2 offset = HAS_BIAS ? fma2(Half2<T>::widen(bw[i]), log2e2, nl2[i]) : nl2[i];
+    float lo, hi;
+    unpack2(fma2(s2, c2, offset), lo, hi);
+    const f32x2 p = pack2(ex2(lo), ex2(hi));
+    p2[i] = p;
+    ds2[i] = mul2(p, add2(d2, nd2[i]));
+  }
+}
+
+__device__ __forceinline__ f32x2 select2(f32x2 v, uint32_t bits, int at) {
+  float lo, hi;
+  unpack2(v, lo, hi);
+  if (((bits >> at) & 1u) == 0) lo = 0.f;
+  if (((bits >> (at + 1)) & 1u) == 0) hi = 0.f;
+  return pack2(lo, hi);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack16(f32x2 v) {
+  float lo, hi;
+  unpack2(v, lo, hi);
+  return Half2<T>::pack(lo, hi);
+}
+
+// ---------------------------------------------------------------------------------------------
 // dQ kernel
 // ---------------------------------------------------------------------------------------------
 
@@ -142,13 +206,16 @@ struct DqSmem {
   static constexpr int k_ready = kv_empty + kRing;       // [kRing]
   static constexpr int bias_full = k_ready + kRing;      // [4]
   static constexpr int bias_empty = bias_full + 4;       // [4]
-  static constexpr int sd_full = bias_empty + 4;         // [2]
-  static constexpr int ds_full = sd_full + 2;            // [2]
-  static constexpr int dq_done = ds_full + 2;            // [2]
+  static constexpr int sd_full = bias_empty + 4;         // [2] S and dP of a step are in tensor memory
+  static constexpr int sd_free = sd_full + 2;            // [2] both have been read into registers
+  static constexpr int ds_full = sd_free + 2;            // [2] dS (16-bit) is in tensor memory
+  static constexpr int ds_done = ds_full + 2;            // [2] the dQ product has consumed it
+  static constexpr int dq_done = ds_done + 2;            // [2] last dQ product finished
   static constexpr int num_bars = dq_done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
-  static constexpr int total = abort_flag + 4;
+  static constexpr int keep = abort_flag + 4;
+  static constexpr int total = keep + kMaxKeepWords * 4;
 };
 constexpr int kDqSmemBytes = DqSmem::total + 1024;
 
@@ -174,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DqSmem::abort_flag);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DqSmem::tmem_slot);
+  uint32_t* keep_words = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::keep);
   auto bar = [&](int index) -> uint32_t { return smem_base + DqSmem::bars + index * 8; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -190,36 +258,51 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   const int KS = P.k_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   const bool has_mask = P.mask != nullptr;
+  const bool has_bits = has_mask || (P.cols % kStep) != 0;
+  // tensor-memory columns of query tile w: S [0,64) | dP [64,128) | dS [128,160) | dQ [160,192)
+  constexpr int kTileCols = 192, kDpCol = 64, kDsCol = 128, kDqCol = 160;
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DqSmem::qd_full + i), 1);
       mbar_init(bar(DqSmem::sd_full + i), 1);
-      mbar_init(bar(DqSmem::ds_full + i), kTile / 32);
+      mbar_init(bar(DqSmem::sd_free + i), 8);
+      mbar_init(bar(DqSmem::ds_full + i), 8);
+      mbar_init(bar(DqSmem::ds_done + i), 1);
       mbar_init(bar(DqSmem::dq_done + i), 1);
     }
     for (int i = 0; i < kRing; ++i) {
       mbar_init(bar(DqSmem::kv_full + i), 1);
       mbar_init(bar(DqSmem::kv_empty + i), 1);
-      mbar_init(bar(DqSmem::k_ready + i), kTile / 32);
+      mbar_init(bar(DqSmem::k_ready + i), 4);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(DqSmem::bias_full + i), 1);
-      mbar_init(bar(DqSmem::bias_empty + i), kTile / 32);
+      mbar_init(bar(DqSmem::bias_empty + i), 8);
     }
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_base + DqSmem::tmem_slot, 512);
     tmem_relinquish();
     tc_fence_before_sync();
+  }
+  if (has_bits && warp < 16) {
+    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+    for (int word = warp; word < KS * 2; word += 16) {
+      const int key = word * 32 + lane;
+      bool keep = key < P.cols;
+      if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+      const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) keep_words[word] = bits;
+    }
   }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       bool ok = true;
       for (int w = 0; w < n_tiles; ++w) {
@@ -247,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
@@ -255,58 +338,70 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       const uint32_t ready_base = has_mask ? DqSmem::k_ready : DqSmem::kv_full;
       bool ok = true;
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
-      for (int j = 0; j <= KS && ok; ++j) {
-        if (j < KS) ok = mbar_wait(bar(ready_base + j % kRing), (j / kRing) & 1, abort_flag);
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          const uint32_t s_t = tmem_base + w * kTile;
-          const uint32_t dp_t = s_t + kStep;
-          const uint32_t dq_t = tmem_base + 2 * kTile + w * kHeadDim;
-          if (j > 0) {
-            const int jj = j - 1, st = jj % kRing;
-            ok = mbar_wait(bar(DqSmem::ds_full + w), jj & 1, abort_flag);
+      // S = Q K^T and dP = dO V^T of step j for query tile w (all operands K-major, 64-byte swizzle)
+      auto issue_scores = [&](int j, int w) {
+        const uint32_t kv = smem_base + DqSmem::kv + (j % kRing) * 2 * kSmallTile;
+        const uint32_t s_t = tmem_base + w * kTileCols;
+        const uint64_t qdesc = smem_desc(smem_base + DqSmem::q + w * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t ddesc = smem_desc(smem_base + DqSmem::dout + w * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t kdesc = smem_desc(kv, 16, 512, kSwizzle64B);
+        const uint64_t vdesc = smem_desc(kv + kSmallTile, 16, 512, kSwizzle64B);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(s_t + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(bar(DqSmem::sd_full + w));
+      };
+      if (ok) ok = mbar_wait(bar(ready_base), 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
+      }
+      for (int j = 0; j < KS && ok; ++j) {
+        if (j + 1 < KS) {
+          ok = mbar_wait(bar(ready_base + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag);
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
-            // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
-            const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
-#pragma unroll
-            for (int kk = 0; kk < kStep / 16; ++kk)
-              mma_ts(dq_t, s_t + kk * 8, kdesc + uint64_t(kk * (1024 >> 4)), idesc_dq, (jj > 0 || kk > 0) ? 1u : 0u);
-            if (jj == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
-            if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
+            issue_scores(j + 1, w);
           }
-          if (j < KS) {
-            const int st = j % kRing;
-            tc_fence_after_sync();
-            const uint32_t kv = smem_base + DqSmem::kv + st * 2 * kSmallTile;
-            const uint64_t qdesc = smem_desc(smem_base + DqSmem::q + w * kBigTile, 16, 512, kSwizzle64B);
-            const uint64_t ddesc = smem_desc(smem_base + DqSmem::dout + w * kBigTile, 16, 512, kSwizzle64B);
-            const uint64_t kdesc = smem_desc(kv, 16, 512, kSwizzle64B);
-            const uint64_t vdesc = smem_desc(kv + kSmallTile, 16, 512, kSwizzle64B);
+        }
+        const int st = j % kRing;
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          ok = mbar_wait(bar(DqSmem::ds_full + w), j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
+          const uint32_t tile_t = tmem_base + w * kTileCols;
+          const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
 #pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)
-              mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)
-              mma_ss(dp_t, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
-            mma_commit(bar(DqSmem::sd_full + w));
-          }
+          for (int kk = 0; kk < kStep / 16; ++kk)
+            mma_ts(tile_t + kDqCol, tile_t + kDsCol + kk * 8, kdesc + uint64_t(kk * (1024 >> 4)), idesc_dq,
+                   (j > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(bar(DqSmem::ds_done + w));
+          if (j == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
+          if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
         }
       }
     }
-  } else if ((warp >> 2) < n_tiles) {
-    const int w = warp >> 2;
+  } else if (warp < 16 && (warp >> 3) < n_tiles) {
+    const int w = warp >> 3;          // query tile
+    const int half = (warp >> 2) & 1; // which 32 of the step's 64 keys
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t s_t = tmem_base + lane_field + w * kTile;
-    const uint32_t dp_t = s_t + kStep;
-    const uint32_t dq_t = tmem_base + lane_field + 2 * kTile + w * kHeadDim;
+    const uint32_t tile_t = tmem_base + lane_field + w * kTileCols;
     const int q_index = q0 + w * kTile + t;
     const bool q_valid = q_index < P.cols;
-    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
     const int64_t stat_at = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index;
     const float neg_lse2 = q_valid ? -P.lse[stat_at] * kLog2e : -INFINITY;
     const float delta = q_valid ? P.delta[stat_at] : 0.f;
     const float scale = P.scale;
+    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
+    const f32x2 nl2[4] = {pack2(neg_lse2, neg_lse2), pack2(neg_lse2, neg_lse2), pack2(neg_lse2, neg_lse2), pack2(neg_lse2, neg_lse2)};
+    const f32x2 nd2[4] = {pack2(-delta, -delta), pack2(-delta, -delta), pack2(-delta, -delta), pack2(-delta, -delta)};
     T* db_row = nullptr;
     bool db_vec = false;
     if (P.dbias_rows && q_valid) {
@@ -316,97 +411,89 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
     bool ok = true;
 
     for (int j = 0; j < KS && ok; ++j) {
-      uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
-      const bool need_bits = has_mask || (j == KS - 1 && (P.cols % kStep) != 0);
-      if (need_bits) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int key = j * kStep + i * 32 + lane;
-          bool keep = key < P.cols;
-          if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
-          bits[i] = __ballot_sync(0xffffffffu, keep);
+      uint32_t my_bits = 0xffffffffu;
+      bool step_all_kept = true;
+      if (has_bits) {
+        const uint2 wds = *reinterpret_cast<const uint2*>(keep_words + j * 2);
+        my_bits = half ? wds.y : wds.x;
+        step_all_kept = (wds.x & wds.y) == 0xffffffffu;
+        if (has_mask && warp < 4) {
+          // Key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory.
+          const int st = j % kRing;
+          if (!step_all_kept) {
+            ok = mbar_wait(bar(DqSmem::kv_full + st), (j / kRing) & 1, abort_flag);
+            if (!ok) break;
+            const uint32_t word = (t < 32) ? wds.x : wds.y;
+            if (t < kStep && ((word >> (t & 31)) & 1u) == 0) {
+              uint4* row = reinterpret_cast<uint4*>(smem_gen + DqSmem::kv + st * 2 * kSmallTile + t * 64);
+              row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+          }
+          mbar_arrive_warp(bar(DqSmem::k_ready + st));
         }
-      }
-      const bool all_kept = (bits[0] & bits[1]) == 0xffffffffu;
-      if (has_mask && w == 0) {
-        // Key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory.
-        const int st = j % kRing;
-        ok = mbar_wait(bar(DqSmem::kv_full + st), (j / kRing) & 1, abort_flag);
-        if (!ok) break;
-        if (!all_kept && t < kStep && ((bits[t >> 5] >> (t & 31)) & 1u) == 0) {
-          uint4* row = reinterpret_cast<uint4*>(smem_gen + DqSmem::kv + st * 2 * kSmallTile + t * 64);
-          row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
-        }
-        fence_proxy_async_smem();
-        mbar_arrive_warp(bar(DqSmem::k_ready + st));
       }
       ok = mbar_wait(bar(DqSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      uint32_t sraw[32], draw[32];
+      tmem_ld32(tile_t + half * 32, sraw);
+      tmem_ld32(tile_t + kDpCol + half * 32, draw);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(DqSmem::sd_free + w));
       const int slot = w * 2 + (j & 1);
       if (HAS_BIAS) {
         ok = mbar_wait(bar(DqSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
         if (!ok) break;
       }
       const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128;
-      uint32_t packed[32];
+      uint32_t packed[16];
+      const int key0 = j * kStep + half * 32;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sraw[32], draw[32];
-        tmem_ld32(s_t + c * 32, sraw);
-        tmem_ld32(dp_t + c * 32, draw);
-        tmem_wait_ld();
-        float ds[32];
+      for (int i8 = 0; i8 < 4; ++i8) {
+        f32x2 p2[4], ds2[4];
+        score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2,
+                                 nd2, p2, ds2);
+        if (my_bits != 0xffffffffu) {
 #pragma unroll
-        for (int i8 = 0; i8 < 4; ++i8) {
-          float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (HAS_BIAS) {
-            const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
-            bv[0] = Half2<T>::lo(v.x); bv[1] = Half2<T>::hi(v.x); bv[2] = Half2<T>::lo(v.y); bv[3] = Half2<T>::hi(v.y);
-            bv[4] = Half2<T>::lo(v.z); bv[5] = Half2<T>::hi(v.z); bv[6] = Half2<T>::lo(v.w); bv[7] = Half2<T>::hi(v.w);
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int i = i8 * 8 + e;
-            const float x = fmaf(__uint_as_float(sraw[i]), scale, bv[e]);
-            const float p = ex2(fmaf(x, kLog2e, neg_lse2));
-            ds[i] = p * (__uint_as_float(draw[i]) - delta);
-          }
-        }
-        if (!all_kept) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (((bits[c] >> i) & 1u) == 0) ds[i] = 0.f;
+          for (int i = 0; i < 4; ++i) ds2[i] = select2(ds2[i], my_bits, i8 * 8 + 2 * i);
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) packed[c * 16 + (i >> 1)] = Half2<T>::pack(ds[i], ds[i + 1]);
+        for (int i = 0; i < 4; ++i) packed[i8 * 4 + i] = pack16<T>(ds2[i]);
         if (db_row) {
-          const int key0 = j * kStep + c * 32;
           if (db_vec && key0 + 32 <= P.cols) {
-            uint4* d4 = reinterpret_cast<uint4*>(db_row + key0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              d4[i] = make_uint4(packed[c * 16 + 4 * i], packed[c * 16 + 4 * i + 1], packed[c * 16 + 4 * i + 2],
-                                 packed[c * 16 + 4 * i + 3]);
+            *reinterpret_cast<uint4*>(db_row + key0 + i8 * 8) =
+                make_uint4(packed[i8 * 4], packed[i8 * 4 + 1], packed[i8 * 4 + 2], packed[i8 * 4 + 3]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (key0 + i < P.cols) db_row[int64_t(key0 + i) * P.db_sk] = T(ds[i]);
+            for (int i = 0; i < 4; ++i) {
+              float lo, hi;
+              unpack2(ds2[i], lo, hi);
+              if (key0 + i8 * 8 + 2 * i < P.cols) db_row[int64_t(key0 + i8 * 8 + 2 * i) * P.db_sk] = T(lo);
+              if (key0 + i8 * 8 + 2 * i + 1 < P.cols) db_row[int64_t(key0 + i8 * 8 + 2 * i + 1) * P.db_sk] = T(hi);
+            }
           }
         }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DqSmem::bias_empty + slot));
-      tmem_st32(s_t, packed);
+      if (j > 0) {
+        // the dQ product of the previous step must have finished reading the dS columns
+        ok = mbar_wait(bar(DqSmem::ds_done + w), (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      tmem_st16(tile_t + kDsCol + half * 16, packed);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::ds_full + w));
     }
 
     if (ok) ok = mbar_wait(bar(DqSmem::dq_done + w), 0, abort_flag);
-    if (ok) {
+    if (ok && half == 0) {
       tc_fence_after_sync();
       uint32_t acc[32];
-      tmem_ld32(dq_t, acc);
+      tmem_ld32(tile_t + kDqCol, acc);
       tmem_wait_ld();
       if (q_valid && P.write_dq) {
         T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
@@ -414,7 +501,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       }
     }
   }
-  teardown(abort_flag, tmem_base, 9);
+  teardown(abort_flag, tmem_base, kMmaWarp);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -426,16 +513,18 @@ struct DkvSmem {
   static constexpr int v = k + 2 * kBigTile;                   // [2] 128 x 32
   static constexpr int qd = v + 2 * kBigTile;                  // [kRing] Q step (4 KiB) + dO step (4 KiB)
   static constexpr int bias = qd + kRing * 2 * kSmallTile;     // [2 tiles][2 buffers] 128 keys x 64 queries
-  static constexpr int stats = bias + 4 * kBiasStep;           // [2 tiles][2 buffers][128 floats]: lse*log2e | delta
-  static constexpr int bars = stats + 4 * 512;
+  static constexpr int stats = bias + 4 * kBiasStep;           // [4 warpgroups][2 buffers][64 floats]: -lse*log2e | delta
+  static constexpr int bars = stats + 8 * 256;
   static constexpr int kv_full = 0;                      // [2]
   static constexpr int qd_full = kv_full + 2;            // [kRing]
   static constexpr int qd_empty = qd_full + kRing;       // [kRing]
   static constexpr int bias_full = qd_empty + kRing;     // [4]
   static constexpr int bias_empty = bias_full + 4;       // [4]
-  static constexpr int sd_full = bias_empty + 4;         // [2]
-  static constexpr int pds_full = sd_full + 2;           // [2]
-  static constexpr int done = pds_full + 2;              // [2]
+  static constexpr int sd_full = bias_empty + 4;         // [2] S^T and dP^T of a step are in tensor memory
+  static constexpr int sd_free = sd_full + 2;            // [2] both have been read into registers
+  static constexpr int pds_full = sd_free + 2;           // [2] P^T and dS^T (16-bit) are in tensor memory
+  static constexpr int pds_done = pds_full + 2;          // [2] the dV / dK products have consumed them
+  static constexpr int done = pds_done + 2;              // [2]
   static constexpr int num_bars = done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
@@ -478,13 +567,17 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
   const int n_tiles = (k0 + kTile < P.cols) ? 2 : 1;
   const int QS = P.q_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
+  // tensor-memory columns of key tile w: S^T [0,64) | dP^T [64,128) | P^T [128,160) | dS^T [160,192) | dK [192,224) | dV [224,256)
+  constexpr int kTileCols = 256, kDpCol = 64, kPCol = 128, kDsCol = 160, kDkCol = 192, kDvCol = 224;
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DkvSmem::kv_full + i), 1);
       mbar_init(bar(DkvSmem::sd_full + i), 1);
-      mbar_init(bar(DkvSmem::pds_full + i), kTile / 32);
+      mbar_init(bar(DkvSmem::sd_free + i), 8);
+      mbar_init(bar(DkvSmem::pds_full + i), 8);
+      mbar_init(bar(DkvSmem::pds_done + i), 1);
       mbar_init(bar(DkvSmem::done + i), 1);
     }
     for (int i = 0; i < kRing; ++i) {
@@ -493,11 +586,11 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(DkvSmem::bias_full + i), 1);
-      mbar_init(bar(DkvSmem::bias_empty + i), kTile / 32);
+      mbar_init(bar(DkvSmem::bias_empty + i), 8);
     }
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_base + DkvSmem::tmem_slot, 512);
     tmem_relinquish();
     tc_fence_before_sync();
@@ -505,9 +598,8 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr int kWgCols = 192;  // S^T 64 | dP^T 64 | dK 32 | dV 32 per key tile
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       bool ok = true;
       for (int w = 0; w < n_tiles; ++w) {
@@ -515,9 +607,11 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
         tma_load_5d(smem_base + DkvSmem::k + w * kBigTile, &P.map_k, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
         tma_load_5d(smem_base + DkvSmem::v + w * kBigTile, &P.map_v, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
       }
+      TA_WAIT_SLOT(wq); TA_WAIT_SLOT(wb);
+      TB_CLOCK(p0);
       for (int j = 0; j < QS && ok; ++j) {
         const int st = j % kRing, round = j / kRing;
-        if (j >= kRing) ok = mbar_wait(bar(DkvSmem::qd_empty + st), (round - 1) & 1, abort_flag);
+        if (j >= kRing) ok = mbar_wait(bar(DkvSmem::qd_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wq));
         if (!ok) break;
         mbar_expect_tx(bar(DkvSmem::qd_full + st), 2 * kSmallTile);
         const uint32_t dst = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
@@ -526,7 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
         if (HAS_BIAS) {
           for (int w = 0; w < n_tiles && ok; ++w) {
             const int slot = w * 2 + (j & 1);
-            if (j >= 2) ok = mbar_wait(bar(DkvSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
+            if (j >= 2) ok = mbar_wait(bar(DkvSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag TA_WAIT_ARG(wb));
             if (!ok) break;
             mbar_expect_tx(bar(DkvSmem::bias_full + slot), kBiasStep);
             // transposed bias: inner axis = query, outer axis = key
@@ -535,151 +629,201 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
           }
         }
       }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(13, wq); TB_ADD(14, wb); TB_ADD(15, clock64() - p0);
+#endif
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
       constexpr uint32_t idesc_acc = instr_desc(fmt, 0, 1, kTile, kHeadDim);
       bool ok = true;
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
-      for (int j = 0; j <= QS && ok; ++j) {
-        if (j < QS) ok = mbar_wait(bar(DkvSmem::qd_full + j % kRing), (j / kRing) & 1, abort_flag);
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          const uint32_t st_t = tmem_base + w * kWgCols;
-          const uint32_t dpt_t = st_t + kStep;
-          const uint32_t dk_t = st_t + 2 * kStep;
-          const uint32_t dv_t = dk_t + kHeadDim;
-          if (j > 0) {
-            const int jj = j - 1, st = jj % kRing;
-            ok = mbar_wait(bar(DkvSmem::pds_full + w), jj & 1, abort_flag);
+      // S^T[128 k x 64 q] = K Q^T and dP^T = V dO^T of step j for key tile w
+      auto issue_scores = [&](int j, int w) {
+        const uint32_t qd = smem_base + DkvSmem::qd + (j % kRing) * 2 * kSmallTile;
+        const uint32_t st_t = tmem_base + w * kTileCols;
+        const uint64_t kdesc = smem_desc(smem_base + DkvSmem::k + w * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t vdesc = smem_desc(smem_base + DkvSmem::v + w * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);
+        const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(st_t, kdesc + uint64_t(kk * 2), qdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(st_t + kDpCol, vdesc + uint64_t(kk * 2), ddesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(bar(DkvSmem::sd_full + w));
+      };
+      if (ok) ok = mbar_wait(bar(DkvSmem::qd_full), 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
+      }
+      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
+#ifdef TA_PROFILE_WAITS
+      long long t_scores = 0, t_acc = 0;
+#endif
+      TB_CLOCK(m0);
+      for (int j = 0; j < QS && ok; ++j) {
+        if (j + 1 < QS) {
+          ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
-            const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);                 // Q step, MN-major
-            const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);    // dO step, MN-major
-#pragma unroll
-            for (int kk = 0; kk < kStep / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 64 q] dO[64 q x 32]
-              mma_ts(dv_t, st_t + kk * 8, ddesc + uint64_t(kk * (1024 >> 4)), idesc_acc, (jj > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-            for (int kk = 0; kk < kStep / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 64 q] Q[64 q x 32]
-              mma_ts(dk_t, dpt_t + kk * 8, qdesc + uint64_t(kk * (1024 >> 4)), idesc_acc, (jj > 0 || kk > 0) ? 1u : 0u);
-            if (jj == QS - 1) mma_commit(bar(DkvSmem::done + w));
-            if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
-          }
-          if (j < QS) {
-            const int st = j % kRing;
-            tc_fence_after_sync();
-            const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
-            const uint64_t kdesc = smem_desc(smem_base + DkvSmem::k + w * kBigTile, 16, 512, kSwizzle64B);
-            const uint64_t vdesc = smem_desc(smem_base + DkvSmem::v + w * kBigTile, 16, 512, kSwizzle64B);
-            const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);
-            const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)  // S^T[128 k x 64 q] = K Q^T
-              mma_ss(st_t, kdesc + uint64_t(kk * 2), qdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)  // dP^T[128 k x 64 q] = V dO^T
-              mma_ss(dpt_t, vdesc + uint64_t(kk * 2), ddesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
-            mma_commit(bar(DkvSmem::sd_full + w));
+            TB_CLOCK(i0);
+            issue_scores(j + 1, w);
+#ifdef TA_PROFILE_WAITS
+            t_scores += clock64() - i0;
+#endif
           }
         }
+        const int st = j % kRing;
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+          if (!ok) break;
+          tc_fence_after_sync();
+          TB_CLOCK(i1);
+          const uint32_t tile_t = tmem_base + w * kTileCols;
+          const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
+          const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);                 // Q step, MN-major
+          const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);    // dO step, MN-major
+#pragma unroll
+          for (int kk = 0; kk < kStep / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 64 q] dO[64 q x 32]
+            mma_ts(tile_t + kDvCol, tile_t + kPCol + kk * 8, ddesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
+                   (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < kStep / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 64 q] Q[64 q x 32]
+            mma_ts(tile_t + kDkCol, tile_t + kDsCol + kk * 8, qdesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
+                   (j > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(bar(DkvSmem::pds_done + w));
+          if (j == QS - 1) mma_commit(bar(DkvSmem::done + w));
+          if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
+#ifdef TA_PROFILE_WAITS
+          t_acc += clock64() - i1;
+#endif
+        }
       }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(6, t_scores); TB_ADD(5, t_acc);
+      TB_ADD(8, wf); TB_ADD(9, wp); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1);
+#endif
     }
-  } else if ((warp >> 2) < n_tiles) {
-    const int w = warp >> 2;
+  } else if (warp < 16 && (warp >> 3) < n_tiles) {
+    const int w = warp >> 3;           // key tile
+    const int half = (warp >> 2) & 1;  // which 32 of the step's 64 queries
+    const int wg = warp >> 2;
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t st_t = tmem_base + lane_field + w * kWgCols;
-    const uint32_t dpt_t = st_t + kStep;
-    const uint32_t dk_t = st_t + 2 * kStep;
-    const uint32_t dv_t = dk_t + kHeadDim;
+    const uint32_t tile_t = tmem_base + lane_field + w * kTileCols;
     const int key = k0 + w * kTile + t;
     bool keep = key < P.cols;
     if (keep && P.mask) keep = P.mask[b * P.m_sb + int64_t(r) * P.m_sr + int64_t(key) * P.m_sc] != 0;
     const float scale = P.scale;
+    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
     const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
     bool ok = true;
 
+#ifdef TA_PROFILE_WAITS
+    const long long loop_start = clock64();
+#endif
+    // Row statistics of the step's queries: thread t < 32 carries -lse*log2e of query t of this warpgroup's half,
+    // thread 32 <= t < 64 carries -delta; the value of step j+1 is fetched while step j is processed.
+    auto fetch_stat = [&](int j) -> float {
+      if (t >= 64 || j >= QS) return 0.f;
+      const int q = j * kStep + half * 32 + (t & 31);
+      if (t < 32) return q < P.cols ? -P.lse[stat_base + q] * kLog2e : -INFINITY;
+      return q < P.cols ? -P.delta[stat_base + q] : 0.f;
+    };
+    float stat_next = fetch_stat(0);
     for (int j = 0; j < QS && ok; ++j) {
-      // stage this step's 64 (lse*log2e, delta) pairs for the warpgroup
-      float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (w * 2 + (j & 1)) * 512);
-      {
-        const int q = j * kStep + (t & 63);
-        float value;
-        if (t < 64) value = q < P.cols ? -P.lse[stat_base + q] * kLog2e : -INFINITY;
-        else value = q < P.cols ? P.delta[stat_base + q] : 0.f;
-        stats[t] = value;
-      }
-      named_barrier_sync(1 + w, kTile);
+      TB_CLOCK(tk0);
+      float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (wg * 2 + (j & 1)) * 256);
+      if (t < 64) stats[t] = stat_next;
+      stat_next = fetch_stat(j + 1);
+      named_barrier_sync(1 + wg, kTile);
+      TB_CLOCK(tk1);
       ok = mbar_wait(bar(DkvSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
+      TB_CLOCK(tk2);
       tc_fence_after_sync();
+      uint32_t sraw[32], draw[32];
+      tmem_ld32(tile_t + half * 32, sraw);
+      tmem_ld32(tile_t + kDpCol + half * 32, draw);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(DkvSmem::sd_free + w));
       const int slot = w * 2 + (j & 1);
+      TB_CLOCK(tk3);
       if (HAS_BIAS) {
         ok = mbar_wait(bar(DkvSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
         if (!ok) break;
       }
+      TB_CLOCK(tk4);
       const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128;
-      uint32_t p_packed[32], ds_packed[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sraw[32], draw[32];
-        tmem_ld32(st_t + c * 32, sraw);
-        tmem_ld32(dpt_t + c * 32, draw);
-        tmem_wait_ld();
+      uint32_t p_packed[16], ds_packed[16];
+      if (keep) {
 #pragma unroll
         for (int i8 = 0; i8 < 4; ++i8) {
-          float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (HAS_BIAS) {
-            const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
-            bv[0] = Half2<T>::lo(v.x); bv[1] = Half2<T>::hi(v.x); bv[2] = Half2<T>::lo(v.y); bv[3] = Half2<T>::hi(v.y);
-            bv[4] = Half2<T>::lo(v.z); bv[5] = Half2<T>::hi(v.z); bv[6] = Half2<T>::lo(v.w); bv[7] = Half2<T>::hi(v.w);
-          }
-          const float4 l0 = *reinterpret_cast<const float4*>(stats + c * 32 + i8 * 8);
-          const float4 l1 = *reinterpret_cast<const float4*>(stats + c * 32 + i8 * 8 + 4);
-          const float4 d0 = *reinterpret_cast<const float4*>(stats + 64 + c * 32 + i8 * 8);
-          const float4 d1 = *reinterpret_cast<const float4*>(stats + 64 + c * 32 + i8 * 8 + 4);
-          const float nl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-          const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-          float pv[8], dv[8];
+          const float4 n01 = *reinterpret_cast<const float4*>(stats + i8 * 8);
+          const float4 n23 = *reinterpret_cast<const float4*>(stats + i8 * 8 + 4);
+          const float4 d01 = *reinterpret_cast<const float4*>(stats + 32 + i8 * 8);
+          const float4 d23 = *reinterpret_cast<const float4*>(stats + 32 + i8 * 8 + 4);
+          const f32x2 nl2[4] = {pack2(n01.x, n01.y), pack2(n01.z, n01.w), pack2(n23.x, n23.y), pack2(n23.z, n23.w)};
+          const f32x2 nd2[4] = {pack2(d01.x, d01.y), pack2(d01.z, d01.w), pack2(d23.x, d23.y), pack2(d23.z, d23.w)};
+          f32x2 p2[4], ds2[4];
+          score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2,
+                                   nd2, p2, ds2);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int i = i8 * 8 + e;
-            const float x = fmaf(__uint_as_float(sraw[i]), scale, bv[e]);
-            const float p = keep ? ex2(fmaf(x, kLog2e, nl[e])) : 0.f;
-            pv[e] = p;
-            dv[e] = keep ? p * (__uint_as_float(draw[i]) - dl[e]) : 0.f;
-          }
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            p_packed[c * 16 + i8 * 4 + (e >> 1)] = Half2<T>::pack(pv[e], pv[e + 1]);
-            ds_packed[c * 16 + i8 * 4 + (e >> 1)] = Half2<T>::pack(dv[e], dv[e + 1]);
+          for (int i = 0; i < 4; ++i) {
+            p_packed[i8 * 4 + i] = pack16<T>(p2[i]);
+            ds_packed[i8 * 4 + i] = pack16<T>(ds2[i]);
           }
         }
+      } else {
+        // a dropped (or out-of-range) key contributes nothing, whatever its row holds
+#pragma unroll
+        for (int i = 0; i < 16; ++i) p_packed[i] = ds_packed[i] = 0u;
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DkvSmem::bias_empty + slot));
-      tmem_st32(st_t, p_packed);
-      tmem_st32(dpt_t, ds_packed);
+      TB_CLOCK(tk5);
+      if (j > 0) {
+        ok = mbar_wait(bar(DkvSmem::pds_done + w), (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      TB_CLOCK(tk6);
+      tmem_st16(tile_t + kPCol + half * 16, p_packed);
+      tmem_st16(tile_t + kDsCol + half * 16, ds_packed);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DkvSmem::pds_full + w));
+#ifdef TA_PROFILE_WAITS
+      if (t == 0) {
+        TB_ADD(3, tk1 - tk0); TB_ADD(0, tk2 - tk1); TB_ADD(1, tk4 - tk3); TB_ADD(4, (tk3 - tk2) + (tk5 - tk4)); TB_ADD(2, tk6 - tk5);
+      }
+#endif
     }
+#ifdef TA_PROFILE_WAITS
+    if (t == 0) { TB_ADD(7, 1); }
+#endif
 
     if (ok) ok = mbar_wait(bar(DkvSmem::done + w), 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       uint32_t acc[32];
-      if (P.write_dk) {
-        tmem_ld32(dk_t, acc);
+      if (half == 0 && P.write_dk) {
+        tmem_ld32(tile_t + kDkCol, acc);
         tmem_wait_ld();
         if (key < P.cols) {
           T* dst = reinterpret_cast<T*>(P.dk.ptr) + b * P.dk.sb + int64_t(r) * P.dk.sr + int64_t(key) * P.dk.sc + h * P.dk.sh;
           store_row32<T>(dst, acc, scale, pair_vec_ok(P.dk));
         }
       }
-      if (P.write_dv) {
-        tmem_ld32(dv_t, acc);
+      if (half == 1 && P.write_dv) {
+        tmem_ld32(tile_t + kDvCol, acc);
         tmem_wait_ld();
         if (key < P.cols) {
           T* dst = reinterpret_cast<T*>(P.dv.ptr) + b * P.dv.sb + int64_t(r) * P.dv.sr + int64_t(key) * P.dv.sc + h * P.dv.sh;
@@ -688,7 +832,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       }
     }
   }
-  teardown(abort_flag, tmem_base, 9);
+  teardown(abort_flag, tmem_base, kMmaWarp);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -758,11 +902,11 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DbSmem::sd_full + i), 1);
-      mbar_init(bar(DbSmem::sd_free + i), 2 * kTile / 32);
+      mbar_init(bar(DbSmem::sd_free + i), 16);
     }
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_base + DbSmem::tmem_slot, 512);
     tmem_relinquish();
     tc_fence_before_sync();
@@ -771,7 +915,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       bool ok = true;
       mbar_expect_tx(bar(DbSmem::bias_full), 2 * kBiasStep);
@@ -789,7 +933,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
         tma_load_5d(dst + 3 * kBigTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kTile);
@@ -816,80 +960,92 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
         mma_commit(bar(DbSmem::row_empty + st));
       }
     }
-  } else {
-    const int w = warp >> 2;  // key half
+  } else if (warp < 16) {
+    const int wg = warp >> 2;  // key quarter: 32 keys
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
     const int q_index = qt * kTile + t;
     const bool q_valid = q_index < P.cols;
-    const int key_base = kt * kTile + w * kStep;
+    const int key_base = kt * kTile + wg * 32;
     const float scale = P.scale;
-    float acc[kStep];
+    f32x2 acc2[16];
 #pragma unroll
-    for (int i = 0; i < kStep; ++i) acc[i] = 0.f;
+    for (int i = 0; i < 16; ++i) acc2[i] = pack2(0.f, 0.f);
+    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
     bool ok = mbar_wait(bar(DbSmem::bias_full), 0, abort_flag);
-    const uint8_t* bias_row = smem_gen + DbSmem::bias + w * kBiasStep + t * 128;
+    // bias tile: two 64-key boxes; this warpgroup reads 16-byte chunks (wg & 1) * 4 .. + 3 of box (wg >> 1)
+    const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128;
+    const bool need_bits = has_mask || key_base + 32 > P.cols;
+    const int64_t stat_stride = int64_t(P.heads) * P.cols;
+    const int64_t stat_first = ((int64_t(b) * P.rows + row_lo) * P.heads + h) * P.cols + q_index;
+    auto load_stats = [&](int i, float& nl, float& dl, bool& keep) {
+      const int r = row_lo + i;
+      nl = -INFINITY;
+      dl = 0.f;
+      keep = false;
+      if (i < n_rows) {
+        if (q_valid) {
+          nl = -P.lse[stat_first + int64_t(i) * stat_stride] * kLog2e;
+          dl = P.delta[stat_first + int64_t(i) * stat_stride];
+        }
+        const int key = key_base + lane;
+        keep = key < P.cols;
+        if (keep && has_mask) keep = P.mask[b * P.m_sb + int64_t(r) * P.m_sr + int64_t(key) * P.m_sc] != 0;
+      }
+    };
+    float neg_lse2, delta, next_nl, next_dl;
+    bool keep_lane, next_keep;
+    load_stats(0, next_nl, next_dl, next_keep);
 
     for (int i = 0; i < n_rows && ok; ++i) {
-      const int r = row_lo + i, buf = i & 1;
-      const int64_t stat_at = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index;
-      const float neg_lse2 = q_valid ? -P.lse[stat_at] * kLog2e : -INFINITY;
-      const float delta = q_valid ? P.delta[stat_at] : 0.f;
-      uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
-      const bool need_bits = has_mask || key_base + kStep > P.cols;
-      if (need_bits) {
-        const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int key = key_base + c * 32 + lane;
-          bool keep = key < P.cols;
-          if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
-          bits[c] = __ballot_sync(0xffffffffu, keep);
-        }
-      }
+      const int buf = i & 1;
+      neg_lse2 = next_nl;
+      delta = next_dl;
+      keep_lane = next_keep;
+      load_stats(i + 1, next_nl, next_dl, next_keep);  // prefetch the next row's statistics and mask byte
+      const uint32_t bits = need_bits ? __ballot_sync(0xffffffffu, keep_lane) : 0xffffffffu;
       ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + w * kStep;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sraw[32], draw[32];
-        tmem_ld32(s_t + c * 32, sraw);
-        tmem_ld32(s_t + kTile + c * 32, draw);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i8 = 0; i8 < 4; ++i8) {
-          const uint4 v = *reinterpret_cast<const uint4*>(bias_row + (((c * 4 + i8) ^ (t & 7)) << 4));
-          const float bv[8] = {Half2<T>::lo(v.x), Half2<T>::hi(v.x), Half2<T>::lo(v.y), Half2<T>::hi(v.y),
-                               Half2<T>::lo(v.z), Half2<T>::hi(v.z), Half2<T>::lo(v.w), Half2<T>::hi(v.w)};
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int n = i8 * 8 + e;
-            const float x = fmaf(__uint_as_float(sraw[n]), scale, bv[e]);
-            const float p = ex2(fmaf(x, kLog2e, neg_lse2));
-            const float ds = p * (__uint_as_float(draw[n]) - delta);
-            const bool kept = (bits[c] >> n) & 1u;
-            acc[c * 32 + n] += kept ? ds : 0.f;
-          }
-        }
-      }
+      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
+      uint32_t sraw[32], draw[32];
+      tmem_ld32(s_t, sraw);
+      tmem_ld32(s_t + kTile, draw);
+      tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DbSmem::sd_free + buf));
+      const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(-delta, -delta);
+      const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
+#pragma unroll
+      for (int i8 = 0; i8 < 4; ++i8) {
+        f32x2 p2[4], ds2[4];
+        score_grad8<T, true>(sraw + i8 * 8, draw + i8 * 8, bias_row + ((((wg & 1) * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2, nd2,
+                             p2, ds2);
+        if (bits != 0xffffffffu) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ds2[i] = select2(ds2[i], bits, i8 * 8 + 2 * i);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc2[i8 * 4 + i] = add2(acc2[i8 * 4 + i], ds2[i]);
+      }
     }
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
     if (ok && q_valid) {
       float* dst = P.parts + (((int64_t(part) * P.batch + b) * P.heads + h) * P.cols + q_index) * P.cols + key_base;
-      if (key_base + kStep <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      if (key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-        for (int i = 0; i < kStep; i += 4)
+        for (int i = 0; i < 32; i += 4)
           *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < kStep; ++i)
+        for (int i = 0; i < 32; ++i)
           if (key_base + i < P.cols) dst[i] = acc[i];
       }
     }
   }
-  teardown(abort_flag, tmem_base, 9);
+  teardown(abort_flag, tmem_base, kMmaWarp);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1119,5 +1275,16 @@ int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oop
 }
 
 int backward_device_status(int reset) { return read_tu_device_status(reset); }
+
+#ifdef TA_PROFILE_WAITS
+extern "C" int oops_ta_debug_bwd_clocks(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_bwd_clk, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long zero[16] = {0};
+    cudaMemcpyToSymbol(g_bwd_clk, zero, sizeof(zero));
+  }
+  return 0;
+}
+#endif
 
 }  // namespace oops_ta

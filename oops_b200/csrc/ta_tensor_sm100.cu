@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
 #ifdef TA_EXP_SKIP_MATH
       uint32_t packed[kKeys / 2];
 #pragma unroll
-      for (int i = 0; i < kKeys / 2; ++i) packed[i] = (uint32_t)(x[i] >> 17) & 0x3f003f00u;
+      for (int i = 0; i < kKeys / 2; ++i) packed[i] = (__float_as_uint(x[i].x) >> 17) & 0x3f003f00u;
       const bool raise = false;
       const float alpha = 1.f;
       l_run = 1.f;
