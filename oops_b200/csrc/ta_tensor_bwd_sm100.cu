@@ -335,9 +335,14 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
       constexpr uint32_t idesc_dq = instr_desc(fmt, 0, 1, kTile, kHeadDim);
-      const uint32_t ready_base = has_mask ? DqSmem::k_ready : DqSmem::kv_full;
       bool ok = true;
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
+      // a K/V step is usable once the copy has landed and, with a mask, once warpgroup 0 has signed it off
+      auto wait_step = [&](int j) -> bool {
+        bool ready = mbar_wait(bar(DqSmem::kv_full + j % kRing), (j / kRing) & 1, abort_flag);
+        if (ready && has_mask) ready = mbar_wait(bar(DqSmem::k_ready + j % kRing), (j / kRing) & 1, abort_flag);
+        return ready;
+      };
       // S = Q K^T and dP = dO V^T of step j for query tile w (all operands K-major, 64-byte swizzle)
       auto issue_scores = [&](int j, int w) {
         const uint32_t kv = smem_base + DqSmem::kv + (j % kRing) * 2 * kSmallTile;
@@ -354,14 +359,14 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
           mma_ss(s_t + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(bar(DqSmem::sd_full + w));
       };
-      if (ok) ok = mbar_wait(bar(ready_base), 0, abort_flag);
+      if (ok) ok = wait_step(0);
       if (ok) {
         tc_fence_after_sync();
         for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
       }
       for (int j = 0; j < KS && ok; ++j) {
         if (j + 1 < KS) {
-          ok = mbar_wait(bar(ready_base + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag);
+          ok = wait_step(j + 1);
           for (int w = 0; w < n_tiles && ok; ++w) {
             ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
             if (!ok) break;
