@@ -160,6 +160,32 @@ int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, co
                      const float* lse, const oops_ta_grads* grads, void* stream);
 
 /*
+ * Forward pass that needs no workspace from the caller and allocates nothing.
+ *
+ * It has no counterpart in the reference.  It is for hosts that cannot hand over scratch memory when
+ * they call: a serving process whose device memory pool was sized and frozen at start-up, a latency-
+ * critical loop that must not run into cudaMalloc's device-wide synchronisation, or code that is in the
+ * middle of recording work and may not touch the allocator.  Same arguments, outputs and numerics as
+ * oops_ta_forward with OOPS_TA_FLAG_FORCE_GENERIC (the layout-agnostic kernels, any dtype, head size
+ * and strides); `problem->workspace` is ignored.  The logits of a block of pair rows are kept in a
+ * fixed array inside the library (oops_ta_forward_static_capacity() bytes, 32 MiB, resident on every
+ * GPU that loads the library until the process exits).
+ *
+ * Limits and rules:
+ *   - one pair row must fit: batch * heads * cols * cols * 4 bytes <= the capacity, otherwise
+ *     OOPS_TA_LIMIT_EXCEEDED is returned and nothing is launched;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture begins;
+ *   - all calls on a device share the one array: calls whose kernels may overlap on the GPU (different
+ *     streams without ordering) race on it -- order them.  Nothing needs clearing between calls;
+ *   - no cudaMalloc/cudaFree or allocating library routine is called.
+ */
+int oops_ta_forward_static(const oops_ta_problem* problem, const oops_ta_pair* out, float* lse, void* stream);
+
+/* Size in bytes of the built-in scratch array used by oops_ta_forward_static. */
+uint64_t oops_ta_forward_static_capacity(void);
+
+/*
  * Device-side status of the current device: OOPS_TA_OK, or OOPS_TA_DEVICE_TIMEOUT if a kernel
  * gave up a bounded wait since the last reset (its outputs are then undefined).  Unlike every
  * other call this one synchronises with the device.  `reset` != 0 clears the word.

@@ -158,6 +158,18 @@ int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, co
   return generic_backward(*problem, *out, *dout, lse, *grads, s);
 }
 
+int oops_ta_forward_static(const oops_ta_problem* problem, const oops_ta_pair* out, float* lse, void* stream) {
+  int status = validate(problem, true);
+  if (status) return status;
+  if (!out || !out->ptr) return fail(OOPS_TA_INVALID_ARGUMENT, "out is NULL");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  return static_forward(*problem, *out, lse, reinterpret_cast<cudaStream_t>(stream));
+}
+
+uint64_t oops_ta_forward_static_capacity(void) { return static_forward_capacity(); }
+
 int oops_ta_device_status(int reset) {
   const int forward = forward_device_status(reset);
   const int backward = backward_device_status(reset);

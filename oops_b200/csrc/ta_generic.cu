@@ -14,6 +14,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "ta_internal.h"
 
@@ -294,9 +295,9 @@ int launch_gemm_dtype(const GemmArgs& g, int dtype, int batch, cudaStream_t stre
   return launch_gemm<EPI, __nv_bfloat16, __nv_bfloat16>(g, batch, stream, what);
 }
 
-int block_rows_for(const oops_ta_problem& p) {
+int block_rows_for(const oops_ta_problem& p, uint64_t budget = kBlockBudget) {
   const uint64_t per_row = uint64_t(p.batch) * p.heads * p.cols * p.cols * sizeof(float);
-  uint64_t rows = std::max<uint64_t>(1, kBlockBudget / std::max<uint64_t>(per_row, 1));
+  uint64_t rows = std::max<uint64_t>(1, budget / std::max<uint64_t>(per_row, 1));
   return (int)std::min<uint64_t>(rows, (uint64_t)p.rows);
 }
 
@@ -351,12 +352,22 @@ uint64_t generic_backward_workspace(const oops_ta_problem& p, const oops_ta_grad
   return total;
 }
 
+namespace {
+int forward_blocks(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, float* logits, int block,
+                   cudaStream_t stream);
+}
+
 int generic_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
   if (p.workspace_bytes < generic_forward_workspace(p) || !p.workspace)
     return fail(OOPS_TA_WORKSPACE_TOO_SMALL, "forward needs %llu scratch bytes, got %llu",
                 (unsigned long long)generic_forward_workspace(p), (unsigned long long)p.workspace_bytes);
-  const int block = block_rows_for(p);
-  float* logits = reinterpret_cast<float*>(p.workspace);
+  return forward_blocks(p, out, lse, reinterpret_cast<float*>(p.workspace), block_rows_for(p), stream);
+}
+
+namespace {
+// Forward pass over blocks of `block` pair rows whose logits live in `logits`.
+int forward_blocks(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, float* logits, int block,
+                   cudaStream_t stream) {
   for (int row0 = 0; row0 < p.rows; row0 += block) {
     const int rows = std::min(block, p.rows - row0);
     GemmArgs s{};
@@ -393,6 +404,55 @@ int generic_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* ls
     if (status) return status;
   }
   return OOPS_TA_OK;
+}
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Forward pass with built-in scratch memory
+// ---------------------------------------------------------------------------------------------
+// Some hosts may not allocate device memory at the time they call in: a serving process whose memory
+// pool was sized and frozen at start-up, a real-time loop where cudaMalloc's implicit device
+// synchronisation is not acceptable, or code that runs between stream-capture begin and end.  For them
+// the logits of a block of rows live in this fixed array instead of a caller-provided workspace.  Every
+// GPU that loads the library holds the array until the process exits, so it is kept modest.
+constexpr uint64_t kStaticScratchBytes = 32ull << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// The array's name is only a host-side handle; kernels need its device address, which differs per device.
+int static_scratch_address(float** address) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex lock;
+  static void* cached[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return fail(OOPS_TA_CUDA_ERROR, "cudaGetDevice failed");
+  std::lock_guard<std::mutex> guard(lock);
+  if (!cached[device]) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || !ptr)
+      return fail(OOPS_TA_CUDA_ERROR, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(err));
+    cached[device] = ptr;
+  }
+  *address = reinterpret_cast<float*>(cached[device]);
+  return OOPS_TA_OK;
+}
+}  // namespace
+
+uint64_t static_forward_capacity() { return kStaticScratchBytes; }
+
+int static_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
+  const uint64_t per_row = uint64_t(p.batch) * p.heads * p.cols * p.cols * sizeof(float);
+  if (per_row > kStaticScratchBytes)
+    return fail(OOPS_TA_LIMIT_EXCEEDED,
+                "one pair row needs batch*heads*cols*cols*4 = %llu scratch bytes, the built-in scratch holds %llu",
+                (unsigned long long)per_row, (unsigned long long)kStaticScratchBytes);
+  float* logits = nullptr;
+  const int status = static_scratch_address(&logits);
+  if (status) return status;
+  // every logit of a block is written before it is read, so nothing has to be cleared between calls
+  return forward_blocks(p, out, lse, logits, block_rows_for(p, kStaticScratchBytes), stream);
 }
 
 int generic_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,

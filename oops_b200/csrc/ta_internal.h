@@ -28,6 +28,10 @@ int generic_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* ls
 int generic_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
                      const oops_ta_grads& g, cudaStream_t stream);
 
+// The layout-agnostic forward pass on the library's built-in scratch array (no caller workspace).
+uint64_t static_forward_capacity();
+int static_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream);
+
 // tcgen05/TMEM/TMA kernels (f16/bf16, head_dim 32, 16-byte aligned rows).
 bool tensor_forward_applies(const oops_ta_problem& p);
 bool tensor_backward_applies(const oops_ta_problem& p, const oops_ta_grads* g);

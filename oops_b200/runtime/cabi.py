@@ -33,6 +33,7 @@ EXPORTS = (
     "oops_ta_abi_version", "oops_ta_status_string", "oops_ta_last_error", "oops_ta_supported",
     "oops_ta_uses_tensor_path", "oops_ta_forward_workspace_bytes", "oops_ta_backward_workspace_bytes",
     "oops_ta_forward", "oops_ta_backward", "oops_ta_launch_count", "oops_ta_device_status",
+    "oops_ta_forward_static", "oops_ta_forward_static_capacity",
 )
 
 
@@ -94,6 +95,9 @@ def library() -> ctypes.CDLL:
     lib.oops_ta_forward.argtypes = [POINTER(Problem), POINTER(Pair), c_void_p, c_void_p]
     lib.oops_ta_backward.restype = c_int
     lib.oops_ta_backward.argtypes = [POINTER(Problem), POINTER(Pair), POINTER(Pair), c_void_p, POINTER(Grads), c_void_p]
+    lib.oops_ta_forward_static.restype = c_int
+    lib.oops_ta_forward_static.argtypes = [POINTER(Problem), POINTER(Pair), c_void_p, c_void_p]
+    lib.oops_ta_forward_static_capacity.restype = c_uint64
     lib.oops_ta_launch_count.restype = c_uint64
     lib.oops_ta_device_status.restype = c_int
     lib.oops_ta_device_status.argtypes = [c_int]
