@@ -518,8 +518,8 @@ struct DkvSmem {
   static constexpr int v = k + 2 * kBigTile;                   // [2] 128 x 32
   static constexpr int qd = v + 2 * kBigTile;                  // [kRing] Q step (4 KiB) + dO step (4 KiB)
   static constexpr int bias = qd + kRing * 2 * kSmallTile;     // [2 tiles][2 buffers] 128 keys x 64 queries
-  static constexpr int stats = bias + 4 * kBiasStep;           // [4 warpgroups][2 buffers][64 floats]: -lse*log2e | delta
-  static constexpr int bars = stats + 8 * 256;
+  static constexpr int stats = bias + 4 * kBiasStep;           // [16 warps][2 buffers][64 floats]: -lse*log2e | -delta
+  static constexpr int bars = stats + 32 * 256;
   static constexpr int kv_full = 0;                      // [2]
   static constexpr int qd_full = kv_full + 2;            // [kRing]
   static constexpr int qd_empty = qd_full + kRing;       // [kRing]
@@ -734,32 +734,31 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
 #ifdef TA_PROFILE_WAITS
     const long long loop_start = clock64();
 #endif
-    // Row statistics of the step's queries: thread t < 32 carries -lse*log2e of query t of this warpgroup's half,
-    // thread 32 <= t < 64 carries -delta; the value of step j+1 is fetched while step j is processed.
-    auto fetch_stat = [&](int j) -> float {
-      if (t >= 64 || j >= QS) return 0.f;
-      const int q = j * kStep + half * 32 + (t & 31);
-      if (t < 32) return q < P.cols ? -P.lse[stat_base + q] * kLog2e : -INFINITY;
-      return q < P.cols ? -P.delta[stat_base + q] : 0.f;
+    // Row statistics of the step's 32 queries of this warpgroup's half: every warp keeps its own copy in shared
+    // memory (no cross-warp barrier): lane i fetches -lse*log2e and -delta of query i one step ahead.
+    auto fetch_stats = [&](int j, float& nl, float& nd) {
+      nl = -INFINITY;
+      nd = 0.f;
+      const int q = j * kStep + half * 32 + lane;
+      if (j < QS && q < P.cols) {
+        nl = -P.lse[stat_base + q] * kLog2e;
+        nd = -P.delta[stat_base + q];
+      }
     };
-    float stat_next = fetch_stat(0);
+    float nl_next, nd_next;
+    fetch_stats(0, nl_next, nd_next);
     for (int j = 0; j < QS && ok; ++j) {
       TB_CLOCK(tk0);
-      float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (wg * 2 + (j & 1)) * 256);
-      if (t < 64) stats[t] = stat_next;
-      stat_next = fetch_stat(j + 1);
-      named_barrier_sync(1 + wg, kTile);
+      float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (warp * 2 + (j & 1)) * 256);
+      stats[lane] = nl_next;
+      stats[32 + lane] = nd_next;
+      fetch_stats(j + 1, nl_next, nd_next);
+      __syncwarp();
       TB_CLOCK(tk1);
       ok = mbar_wait(bar(DkvSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
       TB_CLOCK(tk2);
       tc_fence_after_sync();
-      uint32_t sraw[32], draw[32];
-      tmem_ld32(tile_t + half * 32, sraw);
-      tmem_ld32(tile_t + kDpCol + half * 32, draw);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive_warp(bar(DkvSmem::sd_free + w));
       const int slot = w * 2 + (j & 1);
       TB_CLOCK(tk3);
       if (HAS_BIAS) {
@@ -769,28 +768,41 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       TB_CLOCK(tk4);
       const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128;
       uint32_t p_packed[16], ds_packed[16];
-      if (keep) {
+      // two rounds of 16 queries keep the live registers low; the score columns are released after the second load
 #pragma unroll
-        for (int i8 = 0; i8 < 4; ++i8) {
-          const float4 n01 = *reinterpret_cast<const float4*>(stats + i8 * 8);
-          const float4 n23 = *reinterpret_cast<const float4*>(stats + i8 * 8 + 4);
-          const float4 d01 = *reinterpret_cast<const float4*>(stats + 32 + i8 * 8);
-          const float4 d23 = *reinterpret_cast<const float4*>(stats + 32 + i8 * 8 + 4);
-          const f32x2 nl2[4] = {pack2(n01.x, n01.y), pack2(n01.z, n01.w), pack2(n23.x, n23.y), pack2(n23.z, n23.w)};
-          const f32x2 nd2[4] = {pack2(d01.x, d01.y), pack2(d01.z, d01.w), pack2(d23.x, d23.y), pack2(d23.z, d23.w)};
-          f32x2 p2[4], ds2[4];
-          score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2,
-                                   nd2, p2, ds2);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            p_packed[i8 * 4 + i] = pack16<T>(p2[i]);
-            ds_packed[i8 * 4 + i] = pack16<T>(ds2[i]);
-          }
+      for (int round = 0; round < 2; ++round) {
+        uint32_t sraw[16], draw[16];
+        tmem_ld16(tile_t + half * 32 + round * 16, sraw);
+        tmem_ld16(tile_t + kDpCol + half * 32 + round * 16, draw);
+        tmem_wait_ld();
+        if (round == 1) {
+          tc_fence_before_sync();
+          mbar_arrive_warp(bar(DkvSmem::sd_free + w));
         }
-      } else {
-        // a dropped (or out-of-range) key contributes nothing, whatever its row holds
+        if (keep) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) p_packed[i] = ds_packed[i] = 0u;
+          for (int i8 = 0; i8 < 2; ++i8) {
+            const int c8 = round * 2 + i8;  // which group of 8 queries of this half
+            const float4 n01 = *reinterpret_cast<const float4*>(stats + c8 * 8);
+            const float4 n23 = *reinterpret_cast<const float4*>(stats + c8 * 8 + 4);
+            const float4 d01 = *reinterpret_cast<const float4*>(stats + 32 + c8 * 8);
+            const float4 d23 = *reinterpret_cast<const float4*>(stats + 32 + c8 * 8 + 4);
+            const f32x2 nl2[4] = {pack2(n01.x, n01.y), pack2(n01.z, n01.w), pack2(n23.x, n23.y), pack2(n23.z, n23.w)};
+            const f32x2 nd2[4] = {pack2(d01.x, d01.y), pack2(d01.z, d01.w), pack2(d23.x, d23.y), pack2(d23.z, d23.w)};
+            f32x2 p2[4], ds2[4];
+            score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + c8) ^ (t & 7)) << 4), c2, log2e2,
+                                     nl2, nd2, p2, ds2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
+              ds_packed[c8 * 4 + i] = pack16<T>(ds2[i]);
+            }
+          }
+        } else {
+          // a dropped (or out-of-range) key contributes nothing, whatever its row holds
+#pragma unroll
+          for (int i = 0; i < 8; ++i) p_packed[round * 8 + i] = ds_packed[round * 8 + i] = 0u;
+        }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DkvSmem::bias_empty + slot));
       TB_CLOCK(tk5);
@@ -1013,25 +1025,31 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
-      uint32_t sraw[32], draw[32];
-      tmem_ld32(s_t, sraw);
-      tmem_ld32(s_t + kTile, draw);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive_warp(bar(DbSmem::sd_free + buf));
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(-delta, -delta);
       const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
 #pragma unroll
-      for (int i8 = 0; i8 < 4; ++i8) {
-        f32x2 p2[4], ds2[4];
-        score_grad8<T, true>(sraw + i8 * 8, draw + i8 * 8, bias_row + ((((wg & 1) * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2, nd2,
-                             p2, ds2);
-        if (bits != 0xffffffffu) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) ds2[i] = select2(ds2[i], bits, i8 * 8 + 2 * i);
+      for (int round = 0; round < 2; ++round) {
+        uint32_t sraw[16], draw[16];
+        tmem_ld16(s_t + round * 16, sraw);
+        tmem_ld16(s_t + kTile + round * 16, draw);
+        tmem_wait_ld();
+        if (round == 1) {
+          tc_fence_before_sync();
+          mbar_arrive_warp(bar(DbSmem::sd_free + buf));
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc2[i8 * 4 + i] = add2(acc2[i8 * 4 + i], ds2[i]);
+        for (int i8 = 0; i8 < 2; ++i8) {
+          const int c8 = round * 2 + i8;
+          f32x2 p2[4], ds2[4];
+          score_grad8<T, true>(sraw + i8 * 8, draw + i8 * 8, bias_row + ((((wg & 1) * 4 + c8) ^ (t & 7)) << 4), c2, log2e2, nl2,
+                               nd2, p2, ds2);
+          if (bits != 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ds2[i] = select2(ds2[i], bits, c8 * 8 + 2 * i);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc2[c8 * 4 + i] = add2(acc2[c8 * 4 + i], ds2[i]);
+        }
       }
     }
     float acc[32];
