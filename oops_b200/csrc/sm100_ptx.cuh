@@ -39,6 +39,7 @@ __device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
+constexpr uint32_t kSuspendHintNs = 20000;  // 20 us per probe; the bounded wait below re-probes until its own limit
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
 #ifdef TA_SPIN_TEST_WAIT
@@ -53,14 +54,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 #endif
+  // The suspend-time hint lets the hardware park the warp until the phase completes (or the hint expires)
+  // instead of returning at once, so a waiting warp does not burn issue slots of the warps that compute.
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }
@@ -93,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const uint64_t start = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0x7) == 0) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - start > kWaitLimitNs) {
         *abort_flag = 1;
