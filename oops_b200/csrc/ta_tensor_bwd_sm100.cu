@@ -214,7 +214,8 @@ struct DqSmem {
   static constexpr int num_bars = dq_done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
-  static constexpr int keep = abort_flag + 4;
+  static constexpr int drop_flags = abort_flag + 4;  // [16] per-warp: the mask drops a key of this row
+  static constexpr int keep = drop_flags + 64;
   static constexpr int total = keep + kMaxKeepWords * 4;
 };
 constexpr int kDqSmemBytes = DqSmem::total + 1024;
@@ -288,19 +289,32 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
     tmem_relinquish();
     tc_fence_before_sync();
   }
+  uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::drop_flags);
   if (has_bits && warp < 16) {
     const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+    bool dropped_any = false;
     for (int word = warp; word < KS * 2; word += 16) {
       const int key = word * 32 + lane;
       bool keep = key < P.cols;
-      if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+      if (keep && has_mask) {
+        keep = mask_row[int64_t(key) * P.m_sc] != 0;
+        dropped_any |= !keep;
+      }
       const uint32_t bits = __ballot_sync(0xffffffffu, keep);
       if (lane == 0) keep_words[word] = bits;
     }
+    dropped_any = __any_sync(0xffffffffu, dropped_any);
+    if (lane == 0) drop_flags[warp] = dropped_any ? 1u : 0u;
   }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Key rows only need the sign-off handshake when the mask really drops a key of this row.
+  bool signoff = false;
+  if (has_mask) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) signoff |= drop_flags[i] != 0;
+  }
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
@@ -340,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       // a K/V step is usable once the copy has landed and, with a mask, once warpgroup 0 has signed it off
       auto wait_step = [&](int j) -> bool {
         bool ready = mbar_wait(bar(DqSmem::kv_full + j % kRing), (j / kRing) & 1, abort_flag);
-        if (ready && has_mask) ready = mbar_wait(bar(DqSmem::k_ready + j % kRing), (j / kRing) & 1, abort_flag);
+        if (ready && signoff) ready = mbar_wait(bar(DqSmem::k_ready + j % kRing), (j / kRing) & 1, abort_flag);
         return ready;
       };
       // S = Q K^T and dP = dO V^T of step j for query tile w (all operands K-major, 64-byte swizzle)
@@ -422,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
         const uint2 wds = *reinterpret_cast<const uint2*>(keep_words + j * 2);
         my_bits = half ? wds.y : wds.x;
         step_all_kept = (wds.x & wds.y) == 0xffffffffu;
-        if (has_mask && warp < 4) {
+        if (signoff && warp < 4) {
           // Key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory.
           const int st = j % kRing;
           if (!step_all_kept) {

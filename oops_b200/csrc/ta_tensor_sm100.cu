@@ -55,7 +55,8 @@ struct FwdSmem {
   static constexpr int num_bars = pv_done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
-  static constexpr int keep = abort_flag + 4;          // [kMaxKeepWords] u32
+  static constexpr int drop_flags = abort_flag + 4;    // [8] per-warp: the mask drops a key of this row
+  static constexpr int keep = drop_flags + 32;         // [kMaxKeepWords] u32
   static constexpr int total = keep + kMaxKeepWords * 4;
 };
 #ifdef TA_EXP_ONE_CTA
@@ -144,20 +145,33 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
     tmem_relinquish();
     tc_fence_before_sync();
   }
+  uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + FwdSmem::drop_flags);
   if (has_bits && warp < 8) {
     // one bit per key of this pair row: kept by the mask and inside the row
     const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+    bool dropped_any = false;
     for (int word = warp; word < KS * 2; word += 8) {
       const int key = word * 32 + lane;
       bool keep = key < P.cols;
-      if (keep && has_mask) keep = mask_row[int64_t(key) * P.m_sc] != 0;
+      if (keep && has_mask) {
+        keep = mask_row[int64_t(key) * P.m_sc] != 0;
+        dropped_any |= !keep;
+      }
       const uint32_t bits = __ballot_sync(0xffffffffu, keep);
       if (lane == 0) keep_words[word] = bits;
     }
+    dropped_any = __any_sync(0xffffffffu, dropped_any);
+    if (lane == 0) drop_flags[warp] = dropped_any ? 1u : 0u;
   }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Value rows only need the sign-off handshake when the mask really drops a key of this row.
+  bool signoff = false;
+  if (has_mask) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) signoff |= drop_flags[i] != 0;
+  }
   // tensor-memory columns
   constexpr int kSCol = 0, kPCol = 2 * kKeys, kOCol = 2 * kKeys + 2 * (kKeys / 2);
 
@@ -238,7 +252,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
           if (ok && w == 0) {
             ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
             // with a mask, warpgroup 0 signs off every value step after clearing the rows of dropped keys
-            if (ok && has_mask) ok = mbar_wait(bar(FwdSmem::v_ready + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
+            if (ok && signoff) ok = mbar_wait(bar(FwdSmem::v_ready + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
           }
           if (!ok) break;
           tc_fence_after_sync();
@@ -283,7 +297,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         bits[0] = wds.x; bits[1] = wds.y;
         all_kept = (wds.x & wds.y) == 0xffffffffu;
       }
-      if (has_mask && w == 0) {
+      if (signoff && w == 0) {
         // Values of dropped keys must not reach the tensor core (0 * inf): clear their rows in shared memory.
         // Every step is signed off (one barrier phase per step); only steps with dropped keys are touched.
         const int st = j % kStages;
