@@ -72,6 +72,7 @@ class NestedGeometry:
     prefixes: int
     transposed: bool
     bias_groups: Tuple[int, ...] = ()
+    bias_row_strides: Tuple[int, ...] = ()  # key-axis stride of each sample's bias rows (>= N_i; padded for alignment)
 
     def _cell_starts(self) -> List[int]:
         starts, at = [], 0
@@ -109,14 +110,15 @@ class NestedGeometry:
 
     def bias_views(self, bias: Tensor) -> List[Tensor]:
         prefixes, heads, total = bias.shape
+        row_strides = self.bias_row_strides or self.lengths
         views, at = [], 0
-        for n, groups in zip(self.lengths, self.bias_groups):
+        for n, groups, row in zip(self.lengths, self.bias_groups, row_strides):
             views.append(
                 bias.as_strided(
-                    (prefixes, groups, heads, n, n), (heads * total, n * n, total, n, 1), bias.storage_offset() + at
+                    (prefixes, groups, heads, n, n), (heads * total, n * row, total, row, 1), bias.storage_offset() + at
                 )
             )
-            at += groups * n * n
+            at += groups * n * row
         return views
 
     def lse_sizes(self, query: Tensor) -> List[Tuple[int, int, int, int]]:

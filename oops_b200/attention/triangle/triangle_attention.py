@@ -204,6 +204,9 @@ def _dense(query, key, value, mask, triangle_bias, scale):
     bias5 = None
     if triangle_bias is not None:
         bias5 = batched(triangle_bias).resolve_neg().resolve_conj().contiguous()
+        if bias5.element_size() == 2 and cols % 8 != 0:
+            # 16-byte aligned bias rows (the TMA kernels need them): pad the key axis, then view the first `cols` keys
+            bias5 = torch.nn.functional.pad(bias5, (0, -cols % 8))[..., :cols]
     scale = head_size**-0.5 if scale is None else float(scale)
     out = _function.apply(q5, k5, v5, mask3, bias5, scale, DenseGeometry(), _flags())
     if batchless:
@@ -294,7 +297,7 @@ def _nested_mask(mask, prefix_shape, transposed: bool, lengths) -> Tensor:
     return _broadcast_nested_prefix(values, prefix_shape, 0)
 
 
-def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[Tensor, Tuple[int, ...]]:
+def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[Tensor, Tuple[int, ...], Tuple[int, ...]]:
     """Validate a ragged bias and return it head-major and query-major: ``(P, H, values)`` where each
     sample's block is ordered ``(group, query, key)``, plus the per-sample group counts.
 
@@ -356,16 +359,22 @@ def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[
     values = _broadcast_nested_prefix(values, tuple(prefix_shape), 1)  # (T, *prefix, H)
     values = values.reshape(values.shape[0], -1, num_heads).resolve_neg().resolve_conj()
     prefixes = values.shape[1]
-    if not transposed:
+    # 16-bit biases get 16-byte aligned rows (the TMA kernels need them): the key axis of each sample is padded
+    row_strides = tuple((n + 7) // 8 * 8 if values.element_size() == 2 else n for n in lengths)
+    if not transposed and row_strides == tuple(lengths):
         head_major = values.permute(1, 2, 0).contiguous()
     else:
         pieces, at = [], 0
-        for n, g in zip(lengths, groups):
-            block = values[at : at + g * n * n].reshape(g, n, n, prefixes, num_heads)  # (group, key, query, P, H)
-            pieces.append(block.permute(3, 4, 0, 2, 1).reshape(prefixes, num_heads, g * n * n))
+        for n, g, row in zip(lengths, groups, row_strides):
+            block = values[at : at + g * n * n].reshape(g, n, n, prefixes, num_heads)
+            # stored order is (group, query, key) or, transposed, (group, key, query); target (P, H, group, query, key)
+            block = block.permute(3, 4, 0, 2, 1) if transposed else block.permute(3, 4, 0, 1, 2)
+            if row != n:
+                block = torch.nn.functional.pad(block, (0, row - n))
+            pieces.append(block.reshape(prefixes, num_heads, g * n * row))
             at += g * n * n
         head_major = torch.cat(pieces, dim=2).contiguous()
-    return head_major, groups
+    return head_major, groups, row_strides
 
 
 def _nested(query, key, value, mask, triangle_bias, scale):
@@ -396,9 +405,9 @@ def _nested(query, key, value, mask, triangle_bias, scale):
     mask_values = None
     if mask is not None:
         mask_values = _nested_mask(mask, prefix_shape, transposed, lengths).reshape(total_cells, prefixes).contiguous()
-    bias_values, groups = None, ()
+    bias_values, groups, row_strides = None, (), ()
     if triangle_bias is not None:
-        bias_values, groups = _nested_bias(triangle_bias, num_heads, prefix_shape, lengths)
+        bias_values, groups, row_strides = _nested_bias(triangle_bias, num_heads, prefix_shape, lengths)
     require_same_device(_OPERATOR, query_values, key_values, value_values, mask_values, bias_values)
     _check_admission(
         query_values, key_values, value_values, mask_values, bias_values,
@@ -413,7 +422,10 @@ def _nested(query, key, value, mask, triangle_bias, scale):
     q4 = packed4(query_values)
     k4 = q4 if key_values is query_values else packed4(key_values)
     v4 = q4 if value_values is query_values else k4 if value_values is key_values else packed4(value_values)
-    geometry = NestedGeometry(lengths=lengths, prefixes=prefixes, transposed=transposed, bias_groups=tuple(groups))
+    geometry = NestedGeometry(
+        lengths=lengths, prefixes=prefixes, transposed=transposed, bias_groups=tuple(groups),
+        bias_row_strides=tuple(row_strides),
+    )
     scale = head_size**-0.5 if scale is None else float(scale)
     out = _function.apply(q4, k4, v4, mask_values, bias_values, scale, geometry, _flags())
     return query.packed_like(out.reshape(total_cells, *prefix_shape, num_heads, head_size))

@@ -71,3 +71,29 @@ def test_workspace_queries_are_host_only():
     assert lib.oops_ta_forward_workspace_bytes(ctypes.byref(p)) >= 1 * 8 * 2 * 8 * 8 * 4
     g = cabi.Grads()
     assert lib.oops_ta_backward_workspace_bytes(ctypes.byref(p), ctypes.byref(g)) > 0
+
+
+def _tensor_problem(cols=100, bias_row=104, dtype=cabi.BF16, head_dim=32):
+    p = _problem(dtype=dtype, bias_dtype=dtype, head_dim=head_dim)
+    p.batch, p.rows, p.cols, p.heads = 1, cols, cols, 4
+    for name in ("q", "k", "v"):
+        pair = getattr(p, name)
+        pair.ptr, pair.sh, pair.sc = 0x10000, head_dim, 4 * head_dim
+        pair.sr, pair.sb = cols * 4 * head_dim, cols * cols * 4 * head_dim
+    p.bias_groups, p.bias = 1, 0x20000
+    p.bias_sk, p.bias_sq, p.bias_sh = 1, bias_row, cols * bias_row
+    p.bias_sg = p.bias_sb = 4 * cols * bias_row
+    return p
+
+
+def test_kernel_selection_is_host_only():
+    """Which kernel family serves a problem: tcgen05 for 16-bit, head_dim 32, 16-byte aligned rows."""
+    lib = cabi.library()
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(_tensor_problem()), 0) == 1
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(_tensor_problem()), 1) == 1
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(_tensor_problem(bias_row=100)), 0) == 0  # 200-byte rows
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(_tensor_problem(head_dim=24)), 0) == 0
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(_tensor_problem(dtype=cabi.F32)), 0) == 0
+    forced = _tensor_problem()
+    forced.flags = cabi.FLAG_FORCE_GENERIC
+    assert lib.oops_ta_uses_tensor_path(ctypes.byref(forced), 0) == 0
