@@ -288,5 +288,112 @@ class TriangleAttentionFunction(torch.autograd.Function):
         return dq, dk, dv, None, dbias, None, None, None
 
 
+# ----------------------------------------------------------------------------------------------
+# Dispatcher route: torch.library custom ops with fake (meta) implementations, used under torch.compile and
+# FakeTensorMode, where tensors carry no data pointers.  Takes the place of the reference's
+# `ooperators::_triangle_attention_forward/_backward` ops and their `register_fake` shape functions
+# (oops/attention/triangle/triton/ops.py:156-366).  Eager calls keep the direct autograd.Function above.
+# ----------------------------------------------------------------------------------------------
+
+
+def encode_geometry(geometry) -> List[int]:
+    """Flatten a geometry into integers (custom-op schemas carry no Python objects)."""
+    if isinstance(geometry, DenseGeometry):
+        return []
+    count = len(geometry.lengths)
+    groups = geometry.bias_groups or (0,) * count
+    rows = geometry.bias_row_strides or geometry.lengths
+    return [geometry.prefixes, int(geometry.transposed), count, int(bool(geometry.bias_groups)), *geometry.lengths, *groups,
+            *rows]
+
+
+def decode_geometry(code: Sequence[int]):
+    if len(code) == 0:
+        return DenseGeometry()
+    prefixes, transposed, count, has_bias = (int(v) for v in code[:4])
+    lengths = tuple(int(v) for v in code[4 : 4 + count])
+    groups = tuple(int(v) for v in code[4 + count : 4 + 2 * count]) if has_bias else ()
+    rows = tuple(int(v) for v in code[4 + 2 * count : 4 + 3 * count]) if has_bias else ()
+    return NestedGeometry(lengths=lengths, prefixes=prefixes, transposed=bool(transposed), bias_groups=groups,
+                          bias_row_strides=rows)
+
+
+@torch.library.custom_op("oops_b200::triangle_attention_forward", mutates_args=())
+def _forward_op(
+    query: Tensor, key: Tensor, value: Tensor, mask: Optional[Tensor], bias: Optional[Tensor], scale: float,
+    geometry: List[int], flags: int, want_lse: bool,
+) -> Tuple[Tensor, Tensor]:
+    out, lse = run_forward(decode_geometry(geometry), query, key, value, mask, bias, scale, flags, want_lse)
+    if lse is None:
+        lse = torch.empty(0, dtype=torch.float32, device=query.device)
+    return out, lse
+
+
+@_forward_op.register_fake
+def _forward_fake(query, key, value, mask, bias, scale, geometry, flags, want_lse):
+    out = torch.empty_like(query)
+    count = query.numel() // query.shape[-1] if want_lse else 0
+    return out, query.new_empty((count,), dtype=torch.float32)
+
+
+@torch.library.custom_op("oops_b200::triangle_attention_backward", mutates_args=())
+def _backward_op(
+    grad_out: Tensor, query: Tensor, key: Tensor, value: Tensor, mask: Optional[Tensor], bias: Optional[Tensor],
+    out: Tensor, lse: Tensor, scale: float, geometry: List[int], flags: int, need: List[bool],
+) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    geom = decode_geometry(geometry)
+    query, key, value, out = (geom.canonical_pair(t) for t in (query, key, value, out))
+    grad_out = geom.canonical_pair(grad_out.resolve_neg().to(query.dtype))
+    if bias is not None:
+        bias = geom.canonical_bias(bias)
+    if mask is not None and not isinstance(geom, DenseGeometry):
+        mask = mask.contiguous()
+    grads = run_backward(geom, grad_out, query, key, value, mask, bias, out, lse.contiguous(), scale, flags, need)
+    empty = torch.empty(0, dtype=query.dtype, device=query.device)
+    return tuple(empty if g is None else g for g in grads)
+
+
+@_backward_op.register_fake
+def _backward_fake(grad_out, query, key, value, mask, bias, out, lse, scale, geometry, flags, need):
+    def like(t, wanted):
+        return torch.empty_like(t) if wanted and t is not None else query.new_empty((0,))
+
+    return like(query, need[0]), like(key, need[1]), like(value, need[2]), like(bias, need[3])
+
+
+def _dispatch_setup(ctx, inputs, output):
+    query, key, value, mask, bias, scale, geometry, flags, _want = inputs
+    out, lse = output
+    ctx.save_for_backward(query, key, value, mask, bias, out, lse)
+    ctx.scale, ctx.geometry, ctx.flags = scale, geometry, flags
+    ctx.set_materialize_grads(False)
+
+
+def _dispatch_backward(ctx, grad_out, _grad_lse):
+    if grad_out is None:
+        return (None,) * 9
+    query, key, value, mask, bias, out, lse = ctx.saved_tensors
+    need = [ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2],
+            ctx.needs_input_grad[4] and bias is not None]
+    dq, dk, dv, db = _backward_op(grad_out, query, key, value, mask, bias, out, lse, ctx.scale, ctx.geometry, ctx.flags, need)
+    return (dq if need[0] else None, dk if need[1] else None, dv if need[2] else None, None, db if need[3] else None,
+            None, None, None, None)
+
+
+_forward_op.register_autograd(_dispatch_backward, setup_context=_dispatch_setup)
+
+
+def _needs_dispatcher(*tensors: Optional[Tensor]) -> bool:
+    if torch.compiler.is_compiling():
+        return True
+    from torch._subclasses.fake_tensor import is_fake
+
+    return any(t is not None and is_fake(t) for t in tensors)
+
+
 def apply(query, key, value, mask, bias, scale, geometry, flags=0) -> Tensor:
+    if _needs_dispatcher(query, key, value, mask, bias):
+        want_lse = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (query, key, value, bias))
+        out, _ = _forward_op(query, key, value, mask, bias, scale, encode_geometry(geometry), flags, want_lse)
+        return out
     return TriangleAttentionFunction.apply(query, key, value, mask, bias, scale, geometry, flags)

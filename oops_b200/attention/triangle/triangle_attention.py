@@ -255,18 +255,36 @@ def _broadcast_nested_prefix(values: Tensor, prefix_shape: Tuple[int, ...], tail
     )
 
 
+def _boundaries(nested, level) -> list:
+    """Sample boundaries as Python integers along ragged axis ``level`` (None: the packed axis).
+
+    A container that keeps its shapes on the host hands them over directly (no tensor round trip, and a traced
+    graph stays free of data-dependent reads); otherwise the offset tensors are read back.
+    """
+    host = getattr(nested, "host_offsets", None)
+    if host is not None:
+        return [int(v) for v in host(level)]
+    if level is None:
+        return nested.packed_offsets(dtype=torch.int64).tolist()
+    return nested.ragged_level_offsets(level, dtype=torch.int64).tolist()
+
+
+def _steps(boundaries) -> list:
+    return [boundaries[i + 1] - boundaries[i] for i in range(len(boundaries) - 1)]
+
+
 def _sample_lengths(operand: str, nested) -> Tuple[int, ...]:
     """Per-sample N from the ragged offsets, with the reference's checks (nested.py:34-47)."""
-    rows = nested.ragged_level_offsets(0, dtype=torch.int64)
-    packed = nested.packed_offsets(dtype=torch.int64)
-    if rows.numel() <= 1:
+    rows, packed = _boundaries(nested, 0), _boundaries(nested, None)
+    if len(rows) <= 1:
         raise unsupported(_OPERATOR, "does not serve an empty NestedTensor batch")
-    if packed.shape != rows.shape:
+    if len(packed) != len(rows):
         raise ValueError(f"{_OPERATOR} {operand} packed offsets must contain one boundary per sample")
-    sizes = (rows[1:] - rows[:-1]).tolist()
-    if any(size <= 0 for size in sizes):
-        raise unsupported(_OPERATOR, "requires every nested pair element to have N > 0")
-    if (packed[1:] - packed[:-1]).tolist() != [size * size for size in sizes]:
+    sizes = _steps(rows)
+    for size in sizes:
+        if size <= 0:
+            raise unsupported(_OPERATOR, "requires every nested pair element to have N > 0")
+    if _steps(packed) != [size * size for size in sizes]:
         raise ValueError(f"{_OPERATOR} {operand} token dims must be square (N, N) per sample")
     return tuple(int(size) for size in sizes)
 
@@ -338,21 +356,22 @@ def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[
             _OPERATOR, "requires packed triangle_bias num_heads matching q/k/v", triangle_bias=_describe(packed),
             num_heads=num_heads,
         )
-    packed_offsets = triangle_bias.packed_offsets(dtype=torch.int64)
-    if packed_offsets.numel() != len(lengths) + 1:
+    packed_offsets = _boundaries(triangle_bias, None)
+    if len(packed_offsets) != len(lengths) + 1:
         raise ValueError("triangle_attention triangle_bias must have one packed boundary per sample")
-    counts = (packed_offsets[1:] - packed_offsets[:-1]).tolist()
+    counts = _steps(packed_offsets)
     if shared:
         groups = tuple(1 for _ in lengths)
         if counts != [n * n for n in lengths]:
             raise ValueError("triangle_attention shared triangle_bias layout must match query per sample")
     else:
-        group_offsets = triangle_bias.ragged_level_offsets(0, dtype=torch.int64)
-        if group_offsets.numel() != len(lengths) + 1:
+        group_offsets = _boundaries(triangle_bias, 0)
+        if len(group_offsets) != len(lengths) + 1:
             raise ValueError("triangle_attention triangle_bias must have one packed boundary per sample")
-        groups = tuple(int(g) for g in (group_offsets[1:] - group_offsets[:-1]).tolist())
-        if any(g not in (1, n) for g, n in zip(groups, lengths)):
-            raise ValueError("triangle_attention triangle_bias group axis must be 1 or N_i per sample")
+        groups = tuple(int(g) for g in _steps(group_offsets))
+        for g, n in zip(groups, lengths):
+            if g != 1 and g != n:
+                raise ValueError("triangle_attention triangle_bias group axis must be 1 or N_i per sample")
         if counts != [g * n * n for g, n in zip(groups, lengths)]:
             raise ValueError("triangle_attention triangle_bias query/key axes must both have length N_i per sample")
     values = packed.squeeze(-2) if shared else packed

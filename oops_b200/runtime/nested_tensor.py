@@ -90,18 +90,28 @@ class PackedNestedTensor:
     def __len__(self) -> int:
         return len(self._shapes)
 
-    def ragged_level_offsets(self, level: int = 0, dtype=torch.int64) -> Tensor:
-        axis = self.ragged_dims[level]
+    def host_offsets(self, level: int | None = None) -> list:
+        """Sample boundaries as Python integers: along ragged axis ``level``, or of the packed axis when None.
+
+        The shapes live on the host, so callers that only need lengths (the operator's admission checks, a traced
+        graph) read them here without building a tensor and reading it back.
+        """
         sizes = [0]
         for shape in self._shapes:
-            sizes.append(sizes[-1] + shape[axis])
-        return torch.tensor(sizes, dtype=dtype)
+            if level is None:
+                extent = 1
+                for d in self.ragged_dims:
+                    extent = extent * shape[d]
+            else:
+                extent = shape[self.ragged_dims[level]]
+            sizes.append(sizes[-1] + extent)
+        return sizes
+
+    def ragged_level_offsets(self, level: int = 0, dtype=torch.int64) -> Tensor:
+        return torch.tensor(self.host_offsets(level), dtype=dtype)
 
     def packed_offsets(self, dtype=torch.int64) -> Tensor:
-        sizes = [0]
-        for shape in self._shapes:
-            sizes.append(sizes[-1] + prod(shape[d] for d in self.ragged_dims))
-        return torch.tensor(sizes, dtype=dtype)
+        return torch.tensor(self.host_offsets(None), dtype=dtype)
 
     # -- views ----------------------------------------------------------------------------
     def transpose(self, first: int, second: int) -> "PackedNestedTensor":

@@ -102,3 +102,40 @@ def test_nested_packing_matches_oracle_flatten():
     torch.testing.assert_close(
         swapped.concat, oracle.flatten_nested(torch.unbind(swapped), transposed_pair_axes=True), atol=0, rtol=0
     )
+
+
+def test_fake_tensors_take_the_dispatcher_route():
+    """Shapes and dtypes come from the registered fake implementations; no kernel runs
+    (reference: tests/attention/triangle/test_triangle_attention.py:556-559)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode, is_fake
+
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        q = torch.empty(2, 4, 37, 2, 24, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        swapped = torch.empty(2, 37, 4, 2, 24, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+        bias = torch.empty(2, 1, 2, 37, 37, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        mask = torch.empty(2, 4, 37, device="cuda", dtype=torch.bool)
+        out = triangle_attention(q, swapped, swapped, mask, bias)
+        plain = triangle_attention(q.detach(), swapped, swapped)
+    assert is_fake(out) and out.shape == q.shape and out.dtype == torch.bfloat16 and out.device.type == "cuda"
+    assert out.requires_grad  # the reverse pass of fake CUDA tensors needs a device: covered by the GPU suite
+    assert is_fake(plain) and not plain.requires_grad
+
+
+def test_fake_nested_keeps_the_packing():
+    from torch._subclasses.fake_tensor import FakeTensorMode, is_fake
+
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        q = NestedTensor([torch.empty(n, n, 2, 16, device="cuda") for n in (3, 5)], ragged_dims=(0, 1))
+        bias = NestedTensor([torch.empty(1, 2, n, n, device="cuda") for n in (3, 5)], ragged_dims=(2, 3))
+        out = triangle_attention(q, q, q, None, bias)
+    assert is_fake(out.concat) and out.concat.shape == (34, 2, 16) and out.ragged_dims == q.ragged_dims
+
+
+def test_geometry_survives_the_integer_encoding():
+    from oops_b200.attention.triangle.function import DenseGeometry, decode_geometry, encode_geometry
+
+    nested = NestedGeometry(lengths=(3, 5), prefixes=2, transposed=True, bias_groups=(1, 5), bias_row_strides=(8, 8))
+    assert decode_geometry(encode_geometry(nested)) == nested
+    plain = NestedGeometry(lengths=(7,), prefixes=1, transposed=False)
+    assert decode_geometry(encode_geometry(plain)) == plain
+    assert decode_geometry(encode_geometry(DenseGeometry())) == DenseGeometry()

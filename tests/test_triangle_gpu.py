@@ -457,6 +457,62 @@ def test_nested(cuda, dtype, kwargs):
         assert_within(grad, want[name], atol * max(1.0, float(want[name].abs().max())), f"d{name}")
 
 
+# ----------------------------------------------------------------------------------------------
+# torch.compile and FakeTensorMode (reference: test_triangle_attention.py:225-256 "compile" rows, :556-565 "fake")
+# ----------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("dtype,prefix,bias_kind", [(torch.bfloat16, (2, 2), "full"), (torch.float32, (2,), "shared")])
+def test_compiled_dense(cuda, dtype, prefix, bias_kind):
+    torch._dynamo.reset()
+    execute = torch.compile(lambda *inputs: triangle_attention(*inputs), fullgraph=True, dynamic=True)
+    for cols in (33, 41):
+        case = dense_case(dtype, prefix=prefix, cols=cols, bias_kind=bias_kind)
+        args, leaves = to_device(case, cuda)
+        out = execute(args["q"], args["k"], args["v"], args["mask"], args["bias"])
+        want_out, want_dq, want_dk, want_dv, want_db = oracle_dense(case)
+        assert out.dtype == dtype and out.shape == case["q"].shape
+        assert_within(out, want_out, ATOL[dtype], f"out cols={cols}")
+        grads = torch.autograd.grad(out, [leaves[n] for n in ("q", "k", "v", "bias")], case["upstream"].to(cuda))
+        for name, grad, want in zip(("q", "k", "v", "bias"), grads, (want_dq, want_dk, want_dv, want_db)):
+            scale = 1.0 if dtype is torch.float32 else max(1.0, float(want.abs().max()))
+            assert_within(grad, want, ATOL[dtype] * scale, f"d{name} cols={cols}")
+
+
+def test_compiled_nested(cuda):
+    torch._dynamo.reset()
+
+    def run(*inputs):
+        return triangle_attention(*inputs).concat
+
+    execute = torch.compile(run, fullgraph=True, dynamic=True)
+    for lengths in ((3, 5), (5, 3), (3, 5)):
+        case = nested_case(torch.float32, cuda, lengths=lengths, bias_kind="shared", prefix=(2,), transposed=True)
+        q, k, v, mask, bias, leaves = build_nested(case, cuda)
+        values = execute(q, k, v, mask, bias)
+        upstream = torch.randn(values.shape, generator=torch.Generator().manual_seed(9))
+        want_out, want = nested_oracle(case, upstream)
+        assert_within(values, want_out, ATOL[torch.float32], f"out {lengths}")
+        names = [n for n in ("q", "k", "v", "bias") if n in leaves]
+        grads = torch.autograd.grad(values, [leaves[n] for n in names], upstream.to(cuda))
+        for name, grad in zip(names, grads):
+            assert_within(grad, want[name], ATOL[torch.float32] * max(1.0, float(want[name].abs().max())), f"d{name}")
+
+
+def test_fake_tensor_mode_then_real(cuda):
+    from torch._subclasses.fake_tensor import FakeTensorMode, is_fake
+
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        q, k, v = (torch.randn(2, 4, 37, 2, 24, device=cuda, requires_grad=True) for _ in range(3))
+        bias = torch.randn(2, 1, 2, 37, 37, device=cuda, requires_grad=True)
+        mask = torch.rand(2, 4, 37, device=cuda) > 0.2
+        out = triangle_attention(q, k, v, mask, bias)
+        grads = torch.autograd.grad(out.sum(), (q, k, v, bias))
+    assert is_fake(out) and out.shape == q.shape and out.dtype == q.dtype
+    assert [g.shape for g in grads] == [q.shape, k.shape, v.shape, bias.shape] and all(is_fake(g) for g in grads)
+    run_dense(dense_case(torch.float32, cols=37), cuda)
+
+
 def test_golden_nested(cuda):
     g = torch.load(GOLDEN / "nested.pt", weights_only=False)
     for transposed, key in ((False, "packed"), (True, "packed_transposed")):
