@@ -282,6 +282,26 @@ def main():
         fwd_launches = (cabi.launch_count() - before) // args.steps
     fwd_flops_rank = flops(hi - lo, n, heads, dim, False)
     fwd_tflops = fwd_flops_rank / (ms_fwd * 1e-3) / 1e12
+    # ---- the three reverse-pass tensor kernels, each reached by asking for its gradients only ----
+    # (a call with one group of gradients launches the row-dot kernel, the bias transpose and that one tensor
+    # kernel; the two helpers are ~5 % of the group, so a group's rate slightly understates its tensor kernel)
+    unit = flops(hi - lo, n, heads, dim, False) / 2.0  # one C x C x D product over this rank's rows
+    groups = {}
+    for name, wanted, products in (("dq", "q", 3), ("dkv", "kv", 4), ("dbias", "b", 2)):
+        # only the leaves of this group require gradients, so the reverse call launches this group's kernel alone
+        ql, kl, vl, bl = (t.detach().requires_grad_(c in wanted) for t, c in ((q, "q"), (k, "k"), (v, "v"), (bias_full, "b")))
+        out_l = triangle_attention(ql, kl, vl, mask, bl)
+        targets = [t for t in (ql, kl, vl, bl) if t.requires_grad]
+        run = lambda: torch.autograd.grad(out_l, targets, upstream, retain_graph=True)  # noqa: E731
+        for _ in range(2):
+            run()
+        before = cabi.launch_count()
+        ms = timed(run, args.steps)
+        rate = products * unit / (ms * 1e-3) / 1e12
+        groups[name] = {"ms": ms, "tflops_per_gpu": rate, "frac_of_bf16_peak": rate / peak,
+                        "launches": (cabi.launch_count() - before) // args.steps, "products": products}
+        del out_l, targets, run, ql, kl, vl, bl
+
     profile = {}
     traffic_file = ROOT / "profiles" / "traffic.json"
     if traffic_file.exists():
@@ -289,12 +309,21 @@ def main():
             profile = json.loads(traffic_file.read_text())
         except Exception:  # noqa: BLE001
             profile = {}
-    bytes_per_row = profile.get("forward_dram_bytes_per_row_n%d" % n)
+
+    def traffic(kernel):
+        per_row = profile.get("%s_dram_bytes_per_row_n%d" % (kernel, n))
+        return None if per_row is None else per_row * (hi - lo)
+
+    # the kernel with the largest share of a training step (ncu launch list): dK/dV
     roofline = {
-        "bound": "tensor", "kernel": "forward (one call; %d launch(es))" % fwd_launches,
-        "achieved": fwd_tflops, "peak": peak, "unit": "TFLOP/s", "frac": fwd_tflops / peak,
-        "peak_kind": peak_kind, "ms": ms_fwd,
-        "traffic": None if bytes_per_row is None else bytes_per_row * (hi - lo),
+        "bound": "tensor", "kernel": "ta_bwd_dkv_kernel (timed as the dK/dV-only reverse call: %d launches, the two "
+        "helper kernels ~5 %% of it)" % groups["dkv"]["launches"],
+        "achieved": groups["dkv"]["tflops_per_gpu"], "peak": peak, "unit": "TFLOP/s",
+        "frac": groups["dkv"]["frac_of_bf16_peak"], "peak_kind": peak_kind, "ms": groups["dkv"]["ms"],
+        "traffic": traffic("dkv"),
+        "forward": {"kernel": "ta_fwd_kernel (one call; %d launch(es))" % fwd_launches, "achieved": fwd_tflops,
+                    "frac": fwd_tflops / peak, "ms": ms_fwd, "traffic": traffic("forward")},
+        "dq": groups["dq"], "dbias": groups["dbias"],
     }
 
     line = {

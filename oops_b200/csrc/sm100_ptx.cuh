@@ -54,6 +54,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 #endif
+#ifdef TA_EXP_HOT_ISSUERS
+  if (threadIdx.x >= blockDim.x - 64) {  // the TMA and MMA issuing warps probe without parking
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+  }
+#endif
+#ifdef TA_EXP_NO_HINT
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+#endif
   // The suspend-time hint lets the hardware park the warp until the phase completes (or the hint expires)
   // instead of returning at once, so a waiting warp does not burn issue slots of the warps that compute.
   asm volatile(
@@ -105,6 +131,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
   return true;
+}
+
+// ---- loads that stay where they are written ---------------------------------------------------------
+// A prefetch of next step's operand only hides latency if the load issues before this step's work.  The compiler
+// may sink an ordinary load to its first use (it does when registers are tight); a volatile asm load keeps its
+// place among the other volatile statements (barrier waits, tensor-memory loads).
+__device__ __forceinline__ float ldg_f32_here(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_u8_here(const uint8_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
 }
 
 // ---- proxies and fences ------------------------------------------------------------------------

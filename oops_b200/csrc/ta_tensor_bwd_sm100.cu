@@ -25,7 +25,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 576;
+constexpr int kThreads = 608;                            // dQ and dK/dV kernels: 16 + 3 warps
+constexpr int kDbThreads = 576;                          // shared-bias kernel: 16 + 2 warps
 constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
 constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
 constexpr int kSmallTile = kStep * kHeadDim * 2;        // 4 KiB: 64 x 32 tile
@@ -129,18 +130,20 @@ __device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
 // ---------------------------------------------------------------------------------------------
 // shared pieces of the three tensor kernels
 // ---------------------------------------------------------------------------------------------
-// 576 threads: warps 0-15 are four warpgroups of 128 threads that do the element-wise work, warp 16 is
-// the TMA producer, warp 17 issues the MMAs and owns the tensor-memory allocation.  The element-wise
+// 608 threads: warps 0-15 are four warpgroups of 128 threads that do the element-wise work, warp 16 is
+// the TMA producer, warp 17 issues the score products (S, dP) and owns the tensor-memory allocation, warp 18
+// issues the accumulating products (dQ, or dK and dV); the shared-bias kernel leaves warp 18 idle.  Two issuing
+// threads keep the tensor core fed: neither kind of product waits behind the other's barrier.  The element-wise
 // work of the reverse pass has no reduction along a score row, so the 64 columns of a step are split
 // between two warpgroups that address the same tensor-memory lanes (warp % 4 selects the lanes).
 
-constexpr int kProducerWarp = 16, kMmaWarp = 17;
+constexpr int kProducerWarp = 16, kMmaWarp = 17, kAccWarp = 18;
 
 #ifdef TA_PROFILE_WAITS
 // dK/dV kernel, clocks summed over warpgroups (thread 0 of each): 0 sd_full, 1 bias_full, 2 pds_done, 3 stats+named barrier,
 // 4 compute, 5 store+arrive, 6 loop total, 7 warpgroup count; MMA thread: 8 sd_free, 9 pds_full, 10 qd_full, 11 loop total,
 // 12 CTA count; producer: 13 qd_empty, 14 bias_empty
-__device__ unsigned long long g_bwd_clk[16];
+__device__ unsigned long long g_bwd_clk[48];
 #define TB_ADD(slot, value) atomicAdd(&g_bwd_clk[slot], (unsigned long long)(value))
 #define TB_CLOCK(name) const long long name = clock64()
 #else
@@ -166,12 +169,21 @@ __device__ __forceinline__ void score_grad8(const uint32_t* sraw, const uint32_t
   for (int i = 0; i < 4; ++i) {
     const f32x2 s2 = pack2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1]));
     const f32x2 d2 = pack2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1]));
+#ifdef TA_EXP_BWD_NOMATH
+    p2[i] = s2;
+    ds2[i] = d2;
+#else
     const f32x2 offset = HAS_BIAS ? fma2(Half2<T>::widen(bw[i]), log2e2, nl2[i]) : nl2[i];
     float lo, hi;
     unpack2(fma2(s2, c2, offset), lo, hi);
+#ifdef TA_EXP_NOEXP
+    const f32x2 p = pack2(lo, hi);
+#else
     const f32x2 p = pack2(ex2(lo), ex2(hi));
+#endif
     p2[i] = p;
     ds2[i] = mul2(p, add2(d2, nd2[i]));
+#endif
   }
 }
 
@@ -254,8 +266,13 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
+#ifdef TA_EXP_ONE_TILE
+  const int q0 = qp * kTile;
+  const int n_tiles = 1;
+#else
   const int q0 = qp * 2 * kTile;
   const int n_tiles = (q0 + kTile < P.cols) ? 2 : 1;
+#endif
   const int KS = P.k_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   const bool has_mask = P.mask != nullptr;
@@ -348,7 +365,6 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
-      constexpr uint32_t idesc_dq = instr_desc(fmt, 0, 1, kTile, kHeadDim);
       bool ok = true;
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
       // a K/V step is usable once the copy has landed and, with a mask, once warpgroup 0 has signed it off
@@ -378,21 +394,52 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
         tc_fence_after_sync();
         for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
       }
-      for (int j = 0; j < KS && ok; ++j) {
-        if (j + 1 < KS) {
-          ok = wait_step(j + 1);
-          for (int w = 0; w < n_tiles && ok; ++w) {
-            ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_scores(j + 1, w);
-          }
-        }
-        const int st = j % kRing;
+#ifdef TA_PROFILE_WAITS
+      long long qi_wait = 0, qi_issue = 0;
+      const long long qi_start = clock64();
+#endif
+      for (int j = 0; j + 1 < KS && ok; ++j) {
+        TB_CLOCK(a0);
+        ok = wait_step(j + 1);
         for (int w = 0; w < n_tiles && ok; ++w) {
+          TB_CLOCK(a1);
+          ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          TB_CLOCK(a2);
+          issue_scores(j + 1, w);
+#ifdef TA_PROFILE_WAITS
+          qi_wait += a2 - a1; qi_issue += clock64() - a2;
+#endif
+        }
+      }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(28, qi_wait); TB_ADD(29, qi_issue); TB_ADD(30, clock64() - qi_start); TB_ADD(31, 1);
+#endif
+    }
+  } else if (warp == kAccWarp) {
+    // Second issuing thread: the dQ products.  With its own thread the waits for the warpgroups' dS do not hold up
+    // the next score tiles (and the other way round); the tensor core executes both threads' instructions.
+    if (lane == 0) {
+      constexpr uint32_t idesc_dq = instr_desc(Half2<T>::kFormat, 0, 1, kTile, kHeadDim);
+      bool ok = true;
+#ifdef TA_PROFILE_WAITS
+      long long qa_wait = 0, qa_issue = 0;
+      const long long qa_start = clock64();
+#endif
+      for (int j = 0; j < KS && ok; ++j) {
+        const int st = j % kRing;
+        ok = mbar_wait(bar(DqSmem::kv_full + st), (j / kRing) & 1, abort_flag);
+        if (ok && signoff) ok = mbar_wait(bar(DqSmem::k_ready + st), (j / kRing) & 1, abort_flag);
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          TB_CLOCK(b1);
           ok = mbar_wait(bar(DqSmem::ds_full + w), j & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
+#ifdef TA_PROFILE_WAITS
+          const long long b2 = clock64();
+          qa_wait += b2 - b1;
+#endif
           // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
           const uint32_t tile_t = tmem_base + w * kTileCols;
           const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
@@ -403,8 +450,14 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
           mma_commit(bar(DqSmem::ds_done + w));
           if (j == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
           if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
+#ifdef TA_PROFILE_WAITS
+          qa_issue += clock64() - b2;
+#endif
         }
       }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(32, qa_wait); TB_ADD(33, qa_issue); TB_ADD(34, clock64() - qa_start);
+#endif
     }
   } else if (warp < 16 && (warp >> 3) < n_tiles) {
     const int w = warp >> 3;          // query tile
@@ -428,8 +481,13 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       db_vec = P.db_sk == 1 && (reinterpret_cast<uintptr_t>(db_row) & 15) == 0;
     }
     bool ok = true;
+#ifdef TA_PROFILE_WAITS
+    uint32_t qc[6] = {0, 0, 0, 0, 0, 0};
+    const long long q_loop_start = clock64();
+#endif
 
     for (int j = 0; j < KS && ok; ++j) {
+      TB_CLOCK(qk0);
       uint32_t my_bits = 0xffffffffu;
       bool step_all_kept = true;
       if (has_bits) {
@@ -454,6 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       }
       ok = mbar_wait(bar(DqSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
+      TB_CLOCK(qk1);
       tc_fence_after_sync();
       uint32_t sraw[32], draw[32];
       tmem_ld32(tile_t + half * 32, sraw);
@@ -461,11 +520,13 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::sd_free + w));
+      TB_CLOCK(qk2);
       const int slot = w * 2 + (j & 1);
       if (HAS_BIAS) {
         ok = mbar_wait(bar(DqSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
         if (!ok) break;
       }
+      TB_CLOCK(qk3);
       const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128;
       uint32_t packed[16];
       const int key0 = j * kStep + half * 32;
@@ -496,17 +557,30 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
         }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DqSmem::bias_empty + slot));
+      TB_CLOCK(qk4);
       if (j > 0) {
         // the dQ product of the previous step must have finished reading the dS columns
         ok = mbar_wait(bar(DqSmem::ds_done + w), (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
       }
+      TB_CLOCK(qk5);
       tmem_st16(tile_t + kDsCol + half * 16, packed);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::ds_full + w));
+#ifdef TA_PROFILE_WAITS
+      TB_CLOCK(qk6);
+      qc[0] += uint32_t(qk1 - qk0); qc[1] += uint32_t(qk2 - qk1); qc[2] += uint32_t(qk3 - qk2); qc[3] += uint32_t(qk4 - qk3);
+      qc[4] += uint32_t(qk5 - qk4); qc[5] += uint32_t(qk6 - qk5);
+#endif
     }
+#ifdef TA_PROFILE_WAITS
+    if (t == 0) {
+      for (int i = 0; i < 6; ++i) TB_ADD(20 + i, qc[i]);
+      TB_ADD(26, clock64() - q_loop_start); TB_ADD(27, 1);
+    }
+#endif
 
     if (ok) ok = mbar_wait(bar(DqSmem::dq_done + w), 0, abort_flag);
     if (ok && half == 0) {
@@ -582,8 +656,13 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
+#ifdef TA_EXP_ONE_TILE
+  const int k0 = kp * kTile;
+  const int n_tiles = 1;
+#else
   const int k0 = kp * 2 * kTile;
   const int n_tiles = (k0 + kTile < P.cols) ? 2 : 1;
+#endif
   const int QS = P.q_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   // tensor-memory columns of key tile w: S^T [0,64) | dP^T [64,128) | P^T [128,160) | dS^T [160,192) | dK [192,224) | dV [224,256)
@@ -656,7 +735,6 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
-      constexpr uint32_t idesc_acc = instr_desc(fmt, 0, 1, kTile, kHeadDim);
       bool ok = true;
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
       // S^T[128 k x 64 q] = K Q^T and dP^T = V dO^T of step j for key tile w
@@ -680,26 +758,43 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
         tc_fence_after_sync();
         for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
       }
-      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
+      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wq);
 #ifdef TA_PROFILE_WAITS
-      long long t_scores = 0, t_acc = 0;
+      long long t_scores = 0;
+#endif
+      TB_CLOCK(m0);
+      for (int j = 0; j + 1 < QS && ok; ++j) {
+        ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+        for (int w = 0; w < n_tiles && ok; ++w) {
+          ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
+          if (!ok) break;
+          tc_fence_after_sync();
+          TB_CLOCK(i0);
+          issue_scores(j + 1, w);
+#ifdef TA_PROFILE_WAITS
+          t_scores += clock64() - i0;
+#endif
+        }
+      }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(6, t_scores);
+      TB_ADD(8, wf); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1);
+#endif
+    }
+  } else if (warp == kAccWarp) {
+    // Second issuing thread: the dV and dK products.  With its own thread the waits for the warpgroups' P and dS do
+    // not hold up the next score tiles (and the other way round); the tensor core executes both threads' instructions.
+    if (lane == 0) {
+      constexpr uint32_t idesc_acc = instr_desc(Half2<T>::kFormat, 0, 1, kTile, kHeadDim);
+      bool ok = true;
+      TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
+#ifdef TA_PROFILE_WAITS
+      long long t_acc = 0;
 #endif
       TB_CLOCK(m0);
       for (int j = 0; j < QS && ok; ++j) {
-        if (j + 1 < QS) {
-          ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
-          for (int w = 0; w < n_tiles && ok; ++w) {
-            ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
-            if (!ok) break;
-            tc_fence_after_sync();
-            TB_CLOCK(i0);
-            issue_scores(j + 1, w);
-#ifdef TA_PROFILE_WAITS
-            t_scores += clock64() - i0;
-#endif
-          }
-        }
         const int st = j % kRing;
+        ok = mbar_wait(bar(DkvSmem::qd_full + st), (j / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
         for (int w = 0; w < n_tiles && ok; ++w) {
           ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
           if (!ok) break;
@@ -726,8 +821,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
         }
       }
 #ifdef TA_PROFILE_WAITS
-      TB_ADD(6, t_scores); TB_ADD(5, t_acc);
-      TB_ADD(8, wf); TB_ADD(9, wp); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1);
+      TB_ADD(5, t_acc); TB_ADD(9, wp); TB_ADD(18, clock64() - m0);
 #endif
     }
   } else if (warp < 16 && (warp >> 3) < n_tiles) {
@@ -750,22 +844,26 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
 #endif
     // Row statistics of the step's 32 queries of this warpgroup's half: every warp keeps its own copy in shared
     // memory (no cross-warp barrier): lane i fetches -lse*log2e and -delta of query i one step ahead.
-    auto fetch_stats = [&](int j, float& nl, float& nd) {
-      nl = -INFINITY;
-      nd = 0.f;
+    // The loaded words are not touched until the next step (any arithmetic on them here would wait for the load).
+    auto fetch_stats = [&](int j, float& lse_raw, float& delta_raw) {
+      lse_raw = INFINITY;
+      delta_raw = 0.f;
       const int q = j * kStep + half * 32 + lane;
       if (j < QS && q < P.cols) {
-        nl = -P.lse[stat_base + q] * kLog2e;
-        nd = -P.delta[stat_base + q];
+        lse_raw = ldg_f32_here(P.lse + stat_base + q);
+        delta_raw = ldg_f32_here(P.delta + stat_base + q);
       }
     };
     float nl_next, nd_next;
     fetch_stats(0, nl_next, nd_next);
+#ifdef TA_PROFILE_WAITS
+    uint32_t pc[6] = {0, 0, 0, 0, 0, 0};
+#endif
     for (int j = 0; j < QS && ok; ++j) {
       TB_CLOCK(tk0);
       float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (warp * 2 + (j & 1)) * 256);
-      stats[lane] = nl_next;
-      stats[32 + lane] = nd_next;
+      stats[lane] = -nl_next * kLog2e;
+      stats[32 + lane] = -nd_next;
       fetch_stats(j + 1, nl_next, nd_next);
       __syncwarp();
       TB_CLOCK(tk1);
@@ -832,13 +930,17 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DkvSmem::pds_full + w));
 #ifdef TA_PROFILE_WAITS
-      if (t == 0) {
-        TB_ADD(3, tk1 - tk0); TB_ADD(0, tk2 - tk1); TB_ADD(1, tk4 - tk3); TB_ADD(4, (tk3 - tk2) + (tk5 - tk4)); TB_ADD(2, tk6 - tk5);
-      }
+      TB_CLOCK(tk7);
+      pc[3] += uint32_t(tk1 - tk0); pc[0] += uint32_t(tk2 - tk1); pc[1] += uint32_t(tk4 - tk3);
+      pc[4] += uint32_t((tk3 - tk2) + (tk5 - tk4)); pc[2] += uint32_t(tk6 - tk5); pc[5] += uint32_t(tk7 - tk6);
 #endif
     }
 #ifdef TA_PROFILE_WAITS
-    if (t == 0) { TB_ADD(7, 1); }
+    if (t == 0) {
+      TB_ADD(3, pc[3]); TB_ADD(0, pc[0]); TB_ADD(1, pc[1]); TB_ADD(4, pc[4]); TB_ADD(2, pc[2]); TB_ADD(16, pc[5]);
+      TB_ADD(17, clock64() - loop_start);
+      TB_ADD(7, 1);
+    }
 #endif
 
     if (ok) ok = mbar_wait(bar(DkvSmem::done + w), 0, abort_flag);
@@ -900,7 +1002,7 @@ struct DbParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
+__global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1009,31 +1111,35 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dbias_kernel(const __grid_
     const bool need_bits = has_mask || key_base + 32 > P.cols;
     const int64_t stat_stride = int64_t(P.heads) * P.cols;
     const int64_t stat_first = ((int64_t(b) * P.rows + row_lo) * P.heads + h) * P.cols + q_index;
-    auto load_stats = [&](int i, float& nl, float& dl, bool& keep) {
+    // Prefetch of the next row's statistics and mask byte: the loaded words stay untouched until that row's turn
+    // (any arithmetic on them here would wait for the load).
+    auto load_stats = [&](int i, float& lse_raw, float& delta_raw, uint32_t& keep_raw) {
       const int r = row_lo + i;
-      nl = -INFINITY;
-      dl = 0.f;
-      keep = false;
+      lse_raw = INFINITY;
+      delta_raw = 0.f;
+      keep_raw = 0;
       if (i < n_rows) {
         if (q_valid) {
-          nl = -P.lse[stat_first + int64_t(i) * stat_stride] * kLog2e;
-          dl = P.delta[stat_first + int64_t(i) * stat_stride];
+          lse_raw = ldg_f32_here(P.lse + stat_first + int64_t(i) * stat_stride);
+          delta_raw = ldg_f32_here(P.delta + stat_first + int64_t(i) * stat_stride);
         }
         const int key = key_base + lane;
-        keep = key < P.cols;
-        if (keep && has_mask) keep = P.mask[b * P.m_sb + int64_t(r) * P.m_sr + int64_t(key) * P.m_sc] != 0;
+        if (key < P.cols) {
+          keep_raw = 1;
+          if (has_mask) keep_raw = ldg_u8_here(P.mask + b * P.m_sb + int64_t(r) * P.m_sr + int64_t(key) * P.m_sc);
+        }
       }
     };
-    float neg_lse2, delta, next_nl, next_dl;
-    bool keep_lane, next_keep;
-    load_stats(0, next_nl, next_dl, next_keep);
+    float neg_lse2, delta, next_lse, next_dl;
+    uint32_t next_keep;
+    load_stats(0, next_lse, next_dl, next_keep);
 
     for (int i = 0; i < n_rows && ok; ++i) {
       const int buf = i & 1;
-      neg_lse2 = next_nl;
+      neg_lse2 = -next_lse * kLog2e;
       delta = next_dl;
-      keep_lane = next_keep;
-      load_stats(i + 1, next_nl, next_dl, next_keep);  // prefetch the next row's statistics and mask byte
+      const bool keep_lane = next_keep != 0;
+      load_stats(i + 1, next_lse, next_dl, next_keep);
       const uint32_t bits = need_bits ? __ballot_sync(0xffffffffu, keep_lane) : 0xffffffffu;
       ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
@@ -1189,7 +1295,11 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.bias_groups = p.bias_groups;
+#ifdef TA_EXP_ONE_TILE
+    P.q_pairs = (int)ceil_div(p.cols, kTile);
+#else
     P.q_pairs = (int)ceil_div(p.cols, 2 * kTile);
+#endif
     P.k_steps = (int)ceil_div(p.cols, kStep);
     P.scale = p.scale;
     const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.q_pairs);
@@ -1235,7 +1345,11 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.bias_groups = p.bias_groups;
+#ifdef TA_EXP_ONE_TILE
+    P.k_pairs = (int)ceil_div(p.cols, kTile);
+#else
     P.k_pairs = (int)ceil_div(p.cols, 2 * kTile);
+#endif
     P.q_steps = (int)ceil_div(p.cols, kStep);
     P.scale = p.scale;
     const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.k_pairs);
@@ -1271,7 +1385,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     auto kernel = ta_bwd_dbias_kernel<T>;
     status = reserve_smem(kernel, kDbSmemBytes);
     if (status) return status;
-    kernel<<<grid, kThreads, kDbSmemBytes, stream>>>(P);
+    kernel<<<grid, kDbThreads, kDbSmemBytes, stream>>>(P);
     count_launch();
     status = check_launch("tcgen05 shared-bias gradient");
     if (status) return status;
@@ -1315,9 +1429,9 @@ int backward_device_status(int reset) { return read_tu_device_status(reset); }
 
 #ifdef TA_PROFILE_WAITS
 extern "C" int oops_ta_debug_bwd_clocks(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_bwd_clk, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
+  if (cudaMemcpyFromSymbol(out, g_bwd_clk, sizeof(unsigned long long) * 48) != cudaSuccess) return 1;
   if (reset) {
-    unsigned long long zero[16] = {0};
+    unsigned long long zero[48] = {0};
     cudaMemcpyToSymbol(g_bwd_clk, zero, sizeof(zero));
   }
   return 0;
