@@ -25,7 +25,10 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 608;                            // dQ and dK/dV kernels: 16 + 3 warps
+constexpr int kTilesPerCta = 1;                          // dQ and dK/dV kernels: 128-row tiles owned by one CTA (1 or 2)
+constexpr int kElemWarps = 8 * kTilesPerCta;             // two warpgroups per tile
+constexpr int kThreads = (kElemWarps + (kTilesPerCta == 2 ? 3 : 2)) * 32;
+constexpr int kCtasPerSm = kTilesPerCta == 2 ? 1 : 2;
 constexpr int kDbThreads = 576;                          // shared-bias kernel: 16 + 2 warps
 constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
 constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
@@ -137,7 +140,8 @@ __device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
 // work of the reverse pass has no reduction along a score row, so the 64 columns of a step are split
 // between two warpgroups that address the same tensor-memory lanes (warp % 4 selects the lanes).
 
-constexpr int kProducerWarp = 16, kMmaWarp = 17, kAccWarp = 18;
+constexpr int kProducerWarp = kElemWarps, kMmaWarp = kElemWarps + 1, kAccWarp = kElemWarps + 2;
+constexpr int kDbProducerWarp = 16, kDbMmaWarp = 17;
 
 #ifdef TA_PROFILE_WAITS
 // dK/dV kernel, clocks summed over warpgroups (thread 0 of each): 0 sd_full, 1 bias_full, 2 pds_done, 3 stats+named barrier,
@@ -207,11 +211,11 @@ __device__ __forceinline__ uint32_t pack16(f32x2 v) {
 // ---------------------------------------------------------------------------------------------
 
 struct DqSmem {
-  static constexpr int q = 0;                                 // [2] 128 x 32
-  static constexpr int dout = q + 2 * kBigTile;               // [2] 128 x 32
-  static constexpr int kv = dout + 2 * kBigTile;              // [kRing] K step (4 KiB) + V step (4 KiB)
-  static constexpr int bias = kv + kRing * 2 * kSmallTile;    // [2 tiles][2 buffers] 128 x 64
-  static constexpr int bars = bias + 4 * kBiasStep;
+  static constexpr int q = 0;                                         // [tiles] 128 x 32
+  static constexpr int dout = q + kTilesPerCta * kBigTile;            // [tiles] 128 x 32
+  static constexpr int kv = dout + kTilesPerCta * kBigTile;           // [kRing] K step (4 KiB) + V step (4 KiB)
+  static constexpr int bias = kv + kRing * 2 * kSmallTile;            // [tiles][2 buffers] 128 x 64
+  static constexpr int bars = bias + 2 * kTilesPerCta * kBiasStep;
   static constexpr int qd_full = 0;                      // [2]
   static constexpr int kv_full = qd_full + 2;            // [kRing]
   static constexpr int kv_empty = kv_full + kRing;       // [kRing]
@@ -226,7 +230,7 @@ struct DqSmem {
   static constexpr int num_bars = dq_done + 2;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
-  static constexpr int drop_flags = abort_flag + 4;  // [16] per-warp: the mask drops a key of this row
+  static constexpr int drop_flags = abort_flag + 4;  // [<= 16] per-warp: the mask drops a key of this row
   static constexpr int keep = drop_flags + 64;
   static constexpr int total = keep + kMaxKeepWords * 4;
 };
@@ -248,7 +252,7 @@ struct DqParams {
 };
 
 template <typename T, bool HAS_BIAS>
-__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_constant__ DqParams P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const __grid_constant__ DqParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -266,23 +270,19 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
-#ifdef TA_EXP_ONE_TILE
-  const int q0 = qp * kTile;
-  const int n_tiles = 1;
-#else
-  const int q0 = qp * 2 * kTile;
-  const int n_tiles = (q0 + kTile < P.cols) ? 2 : 1;
-#endif
+  const int q0 = qp * kTilesPerCta * kTile;
+  const int n_tiles = (kTilesPerCta == 2 && q0 + kTile < P.cols) ? 2 : 1;
   const int KS = P.k_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   const bool has_mask = P.mask != nullptr;
   const bool has_bits = has_mask || (P.cols % kStep) != 0;
   // tensor-memory columns of query tile w: S [0,64) | dP [64,128) | dS [128,160) | dQ [160,192)
   constexpr int kTileCols = 192, kDpCol = 64, kDsCol = 128, kDqCol = 160;
+  constexpr int kTmemCols = kTilesPerCta == 2 ? 512 : 256;
 
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kTilesPerCta; ++i) {
       mbar_init(bar(DqSmem::qd_full + i), 1);
       mbar_init(bar(DqSmem::sd_full + i), 1);
       mbar_init(bar(DqSmem::sd_free + i), 8);
@@ -295,22 +295,22 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       mbar_init(bar(DqSmem::kv_empty + i), 1);
       mbar_init(bar(DqSmem::k_ready + i), 4);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2 * kTilesPerCta; ++i) {
       mbar_init(bar(DqSmem::bias_full + i), 1);
       mbar_init(bar(DqSmem::bias_empty + i), 8);
     }
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_base + DqSmem::tmem_slot, 512);
+    tmem_alloc(smem_base + DqSmem::tmem_slot, kTmemCols);
     tmem_relinquish();
     tc_fence_before_sync();
   }
   uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::drop_flags);
-  if (has_bits && warp < 16) {
+  if (has_bits && warp < kElemWarps) {
     const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
     bool dropped_any = false;
-    for (int word = warp; word < KS * 2; word += 16) {
+    for (int word = warp; word < KS * 2; word += kElemWarps) {
       const int key = word * 32 + lane;
       bool keep = key < P.cols;
       if (keep && has_mask) {
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
   bool signoff = false;
   if (has_mask) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) signoff |= drop_flags[i] != 0;
+    for (int i = 0; i < kElemWarps; ++i) signoff |= drop_flags[i] != 0;
   }
 
   if (warp == kProducerWarp) {
@@ -361,12 +361,16 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
         }
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || (kTilesPerCta == 2 && warp == kAccWarp)) {
+    // One tile per CTA: one thread issues everything in the order the events arrive (scores of step j+1 when the
+    // warpgroups have read step j, dQ of step j when they have stored dS).  Two tiles per CTA: a second thread issues
+    // the dQ products, so that neither kind of product waits behind the other tile's barrier.
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
+      constexpr uint32_t idesc_dq = instr_desc(fmt, 0, 1, kTile, kHeadDim);
+      const bool do_scores = warp == kMmaWarp, do_acc = kTilesPerCta == 1 || warp == kAccWarp;
       bool ok = true;
-      for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
       // a K/V step is usable once the copy has landed and, with a mask, once warpgroup 0 has signed it off
       auto wait_step = [&](int j) -> bool {
         bool ready = mbar_wait(bar(DqSmem::kv_full + j % kRing), (j / kRing) & 1, abort_flag);
@@ -389,77 +393,49 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
           mma_ss(s_t + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(bar(DqSmem::sd_full + w));
       };
-      if (ok) ok = wait_step(0);
-      if (ok) {
-        tc_fence_after_sync();
-        for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
-      }
-#ifdef TA_PROFILE_WAITS
-      long long qi_wait = 0, qi_issue = 0;
-      const long long qi_start = clock64();
-#endif
-      for (int j = 0; j + 1 < KS && ok; ++j) {
-        TB_CLOCK(a0);
-        ok = wait_step(j + 1);
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          TB_CLOCK(a1);
-          ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          TB_CLOCK(a2);
-          issue_scores(j + 1, w);
-#ifdef TA_PROFILE_WAITS
-          qi_wait += a2 - a1; qi_issue += clock64() - a2;
-#endif
-        }
-      }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(28, qi_wait); TB_ADD(29, qi_issue); TB_ADD(30, clock64() - qi_start); TB_ADD(31, 1);
-#endif
-    }
-  } else if (warp == kAccWarp) {
-    // Second issuing thread: the dQ products.  With its own thread the waits for the warpgroups' dS do not hold up
-    // the next score tiles (and the other way round); the tensor core executes both threads' instructions.
-    if (lane == 0) {
-      constexpr uint32_t idesc_dq = instr_desc(Half2<T>::kFormat, 0, 1, kTile, kHeadDim);
-      bool ok = true;
-#ifdef TA_PROFILE_WAITS
-      long long qa_wait = 0, qa_issue = 0;
-      const long long qa_start = clock64();
-#endif
-      for (int j = 0; j < KS && ok; ++j) {
+      // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
+      auto issue_dq = [&](int j, int w) {
         const int st = j % kRing;
-        ok = mbar_wait(bar(DqSmem::kv_full + st), (j / kRing) & 1, abort_flag);
-        if (ok && signoff) ok = mbar_wait(bar(DqSmem::k_ready + st), (j / kRing) & 1, abort_flag);
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          TB_CLOCK(b1);
-          ok = mbar_wait(bar(DqSmem::ds_full + w), j & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-#ifdef TA_PROFILE_WAITS
-          const long long b2 = clock64();
-          qa_wait += b2 - b1;
-#endif
-          // dQ[128 x 32] += dS[128 x 64] K[64 x 32]; K is MN-major (channel contiguous).
-          const uint32_t tile_t = tmem_base + w * kTileCols;
-          const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
+        const uint32_t tile_t = tmem_base + w * kTileCols;
+        const uint64_t kdesc = smem_desc(smem_base + DqSmem::kv + st * 2 * kSmallTile, 16, 512, kSwizzle64B);
 #pragma unroll
-          for (int kk = 0; kk < kStep / 16; ++kk)
-            mma_ts(tile_t + kDqCol, tile_t + kDsCol + kk * 8, kdesc + uint64_t(kk * (1024 >> 4)), idesc_dq,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(bar(DqSmem::ds_done + w));
-          if (j == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
-          if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
-#ifdef TA_PROFILE_WAITS
-          qa_issue += clock64() - b2;
-#endif
+        for (int kk = 0; kk < kStep / 16; ++kk)
+          mma_ts(tile_t + kDqCol, tile_t + kDsCol + kk * 8, kdesc + uint64_t(kk * (1024 >> 4)), idesc_dq,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(bar(DqSmem::ds_done + w));
+        if (j == KS - 1) mma_commit(bar(DqSmem::dq_done + w));
+        if (w == n_tiles - 1) mma_commit(bar(DqSmem::kv_empty + st));
+      };
+      if (do_scores) {
+        for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DqSmem::qd_full + w), 0, abort_flag);
+        if (ok) ok = wait_step(0);
+        if (ok) {
+          tc_fence_after_sync();
+          for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
         }
       }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(32, qa_wait); TB_ADD(33, qa_issue); TB_ADD(34, clock64() - qa_start);
-#endif
+      for (int j = 0; j < KS && ok; ++j) {
+        if (do_scores && j + 1 < KS) {
+          ok = wait_step(j + 1);
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DqSmem::sd_free + w), j & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_scores(j + 1, w);
+          }
+        }
+        if (do_acc && ok) {
+          if (!do_scores) ok = wait_step(j);
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DqSmem::ds_full + w), j & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_dq(j, w);
+          }
+        }
+      }
     }
-  } else if (warp < 16 && (warp >> 3) < n_tiles) {
+  } else if (warp < kElemWarps && (warp >> 3) < n_tiles) {
     const int w = warp >> 3;          // query tile
     const int half = (warp >> 2) & 1; // which 32 of the step's 64 keys
     const int t = tid & (kTile - 1);
@@ -594,7 +570,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
       }
     }
   }
-  teardown(abort_flag, tmem_base, kMmaWarp);
+  teardown(abort_flag, tmem_base, kMmaWarp, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -602,12 +578,12 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dq_kernel(const __grid_con
 // ---------------------------------------------------------------------------------------------
 
 struct DkvSmem {
-  static constexpr int k = 0;                                  // [2] 128 x 32
-  static constexpr int v = k + 2 * kBigTile;                   // [2] 128 x 32
-  static constexpr int qd = v + 2 * kBigTile;                  // [kRing] Q step (4 KiB) + dO step (4 KiB)
-  static constexpr int bias = qd + kRing * 2 * kSmallTile;     // [2 tiles][2 buffers] 128 keys x 64 queries
-  static constexpr int stats = bias + 4 * kBiasStep;           // [16 warps][2 buffers][64 floats]: -lse*log2e | -delta
-  static constexpr int bars = stats + 32 * 256;
+  static constexpr int k = 0;                                          // [tiles] 128 x 32
+  static constexpr int v = k + kTilesPerCta * kBigTile;                // [tiles] 128 x 32
+  static constexpr int qd = v + kTilesPerCta * kBigTile;               // [kRing] Q step (4 KiB) + dO step (4 KiB)
+  static constexpr int bias = qd + kRing * 2 * kSmallTile;             // [tiles][2 buffers] 128 keys x 64 queries
+  static constexpr int stats = bias + 2 * kTilesPerCta * kBiasStep;    // [warps][2 buffers][64 floats]: -lse*log2e | -delta
+  static constexpr int bars = stats + 2 * kElemWarps * 256;
   static constexpr int kv_full = 0;                      // [2]
   static constexpr int qd_full = kv_full + 2;            // [kRing]
   static constexpr int qd_empty = qd_full + kRing;       // [kRing]
@@ -639,7 +615,7 @@ struct DkvParams {
 };
 
 template <typename T, bool HAS_BIAS>
-__global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_constant__ DkvParams P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const __grid_constant__ DkvParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -656,21 +632,17 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
-#ifdef TA_EXP_ONE_TILE
-  const int k0 = kp * kTile;
-  const int n_tiles = 1;
-#else
-  const int k0 = kp * 2 * kTile;
-  const int n_tiles = (k0 + kTile < P.cols) ? 2 : 1;
-#endif
+  const int k0 = kp * kTilesPerCta * kTile;
+  const int n_tiles = (kTilesPerCta == 2 && k0 + kTile < P.cols) ? 2 : 1;
   const int QS = P.q_steps;
   const int g = P.bias_groups == 1 ? 0 : r;
   // tensor-memory columns of key tile w: S^T [0,64) | dP^T [64,128) | P^T [128,160) | dS^T [160,192) | dK [192,224) | dV [224,256)
   constexpr int kTileCols = 256, kDpCol = 64, kPCol = 128, kDsCol = 160, kDkCol = 192, kDvCol = 224;
+  constexpr int kTmemCols = kTilesPerCta * kTileCols;
 
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kTilesPerCta; ++i) {
       mbar_init(bar(DkvSmem::kv_full + i), 1);
       mbar_init(bar(DkvSmem::sd_full + i), 1);
       mbar_init(bar(DkvSmem::sd_free + i), 8);
@@ -682,14 +654,14 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       mbar_init(bar(DkvSmem::qd_full + i), 1);
       mbar_init(bar(DkvSmem::qd_empty + i), 1);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2 * kTilesPerCta; ++i) {
       mbar_init(bar(DkvSmem::bias_full + i), 1);
       mbar_init(bar(DkvSmem::bias_empty + i), 8);
     }
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_base + DkvSmem::tmem_slot, 512);
+    tmem_alloc(smem_base + DkvSmem::tmem_slot, kTmemCols);
     tmem_relinquish();
     tc_fence_before_sync();
   }
@@ -731,12 +703,16 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       TB_ADD(13, wq); TB_ADD(14, wb); TB_ADD(15, clock64() - p0);
 #endif
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || (kTilesPerCta == 2 && warp == kAccWarp)) {
+    // One tile per CTA: one thread issues everything in the order the events arrive (scores of step j+1 when the
+    // warpgroups have read step j, dV and dK of step j when they have stored P and dS).  Two tiles per CTA: a second
+    // thread issues the dV/dK products, so that neither kind of product waits behind the other tile's barrier.
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_s = instr_desc(fmt, 0, 0, kTile, kStep);
+      constexpr uint32_t idesc_acc = instr_desc(fmt, 0, 1, kTile, kHeadDim);
+      const bool do_scores = warp == kMmaWarp, do_acc = kTilesPerCta == 1 || warp == kAccWarp;
       bool ok = true;
-      for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
       // S^T[128 k x 64 q] = K Q^T and dP^T = V dO^T of step j for key tile w
       auto issue_scores = [&](int j, int w) {
         const uint32_t qd = smem_base + DkvSmem::qd + (j % kRing) * 2 * kSmallTile;
@@ -753,78 +729,71 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
           mma_ss(st_t + kDpCol, vdesc + uint64_t(kk * 2), ddesc + uint64_t(kk * 2), idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(bar(DkvSmem::sd_full + w));
       };
-      if (ok) ok = mbar_wait(bar(DkvSmem::qd_full), 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
-      }
-      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wq);
+      auto issue_acc = [&](int j, int w) {
+        const int st = j % kRing;
+        const uint32_t tile_t = tmem_base + w * kTileCols;
+        const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
+        const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);                 // Q step, MN-major
+        const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);    // dO step, MN-major
+#pragma unroll
+        for (int kk = 0; kk < kStep / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 64 q] dO[64 q x 32]
+          mma_ts(tile_t + kDvCol, tile_t + kPCol + kk * 8, ddesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kStep / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 64 q] Q[64 q x 32]
+          mma_ts(tile_t + kDkCol, tile_t + kDsCol + kk * 8, qdesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(bar(DkvSmem::pds_done + w));
+        if (j == QS - 1) mma_commit(bar(DkvSmem::done + w));
+        if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
+      };
+      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
 #ifdef TA_PROFILE_WAITS
-      long long t_scores = 0;
+      long long t_scores = 0, t_acc = 0;
 #endif
-      TB_CLOCK(m0);
-      for (int j = 0; j + 1 < QS && ok; ++j) {
-        ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
-          if (!ok) break;
+      if (do_scores) {
+        for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
+        if (ok) ok = mbar_wait(bar(DkvSmem::qd_full), 0, abort_flag);
+        if (ok) {
           tc_fence_after_sync();
-          TB_CLOCK(i0);
-          issue_scores(j + 1, w);
-#ifdef TA_PROFILE_WAITS
-          t_scores += clock64() - i0;
-#endif
+          for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
         }
       }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(6, t_scores);
-      TB_ADD(8, wf); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1);
-#endif
-    }
-  } else if (warp == kAccWarp) {
-    // Second issuing thread: the dV and dK products.  With its own thread the waits for the warpgroups' P and dS do
-    // not hold up the next score tiles (and the other way round); the tensor core executes both threads' instructions.
-    if (lane == 0) {
-      constexpr uint32_t idesc_acc = instr_desc(Half2<T>::kFormat, 0, 1, kTile, kHeadDim);
-      bool ok = true;
-      TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
-#ifdef TA_PROFILE_WAITS
-      long long t_acc = 0;
-#endif
       TB_CLOCK(m0);
       for (int j = 0; j < QS && ok; ++j) {
-        const int st = j % kRing;
-        ok = mbar_wait(bar(DkvSmem::qd_full + st), (j / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
-        for (int w = 0; w < n_tiles && ok; ++w) {
-          ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
-          if (!ok) break;
-          tc_fence_after_sync();
-          TB_CLOCK(i1);
-          const uint32_t tile_t = tmem_base + w * kTileCols;
-          const uint32_t qd = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
-          const uint64_t qdesc = smem_desc(qd, 16, 512, kSwizzle64B);                 // Q step, MN-major
-          const uint64_t ddesc = smem_desc(qd + kSmallTile, 16, 512, kSwizzle64B);    // dO step, MN-major
-#pragma unroll
-          for (int kk = 0; kk < kStep / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 64 q] dO[64 q x 32]
-            mma_ts(tile_t + kDvCol, tile_t + kPCol + kk * 8, ddesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < kStep / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 64 q] Q[64 q x 32]
-            mma_ts(tile_t + kDkCol, tile_t + kDsCol + kk * 8, qdesc + uint64_t(kk * (1024 >> 4)), idesc_acc,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(bar(DkvSmem::pds_done + w));
-          if (j == QS - 1) mma_commit(bar(DkvSmem::done + w));
-          if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
+        if (do_scores && j + 1 < QS) {
+          ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
+            if (!ok) break;
+            tc_fence_after_sync();
+            TB_CLOCK(i0);
+            issue_scores(j + 1, w);
 #ifdef TA_PROFILE_WAITS
-          t_acc += clock64() - i1;
+            t_scores += clock64() - i0;
 #endif
+          }
+        }
+        if (do_acc && ok) {
+          if (!do_scores) ok = mbar_wait(bar(DkvSmem::qd_full + j % kRing), (j / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+          for (int w = 0; w < n_tiles && ok; ++w) {
+            ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+            if (!ok) break;
+            tc_fence_after_sync();
+            TB_CLOCK(i1);
+            issue_acc(j, w);
+#ifdef TA_PROFILE_WAITS
+            t_acc += clock64() - i1;
+#endif
+          }
         }
       }
 #ifdef TA_PROFILE_WAITS
-      TB_ADD(5, t_acc); TB_ADD(9, wp); TB_ADD(18, clock64() - m0);
+      if (do_scores) { TB_ADD(6, t_scores); TB_ADD(8, wf); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1); }
+      if (do_acc) { TB_ADD(5, t_acc); TB_ADD(9, wp); TB_ADD(18, clock64() - m0); }
 #endif
     }
-  } else if (warp < 16 && (warp >> 3) < n_tiles) {
+  } else if (warp < kElemWarps && (warp >> 3) < n_tiles) {
     const int w = warp >> 3;           // key tile
     const int half = (warp >> 2) & 1;  // which 32 of the step's 64 queries
     const int wg = warp >> 2;
@@ -965,7 +934,7 @@ __global__ void __launch_bounds__(kThreads, 1) ta_bwd_dkv_kernel(const __grid_co
       }
     }
   }
-  teardown(abort_flag, tmem_base, kMmaWarp);
+  teardown(abort_flag, tmem_base, kMmaWarp, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1039,7 +1008,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
     }
     fence_barrier_init();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kDbMmaWarp) {
     tmem_alloc(smem_base + DbSmem::tmem_slot, 512);
     tmem_relinquish();
     tc_fence_before_sync();
@@ -1048,7 +1017,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == kProducerWarp) {
+  if (warp == kDbProducerWarp) {
     if (lane == 0) {
       bool ok = true;
       mbar_expect_tx(bar(DbSmem::bias_full), 2 * kBiasStep);
@@ -1066,7 +1035,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
         tma_load_5d(dst + 3 * kBigTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kDbMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kTile);
@@ -1188,7 +1157,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       }
     }
   }
-  teardown(abort_flag, tmem_base, kMmaWarp);
+  teardown(abort_flag, tmem_base, kDbMmaWarp);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1295,11 +1264,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.bias_groups = p.bias_groups;
-#ifdef TA_EXP_ONE_TILE
-    P.q_pairs = (int)ceil_div(p.cols, kTile);
-#else
-    P.q_pairs = (int)ceil_div(p.cols, 2 * kTile);
-#endif
+    P.q_pairs = (int)ceil_div(p.cols, kTilesPerCta * kTile);
     P.k_steps = (int)ceil_div(p.cols, kStep);
     P.scale = p.scale;
     const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.q_pairs);
@@ -1345,11 +1310,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.bias_groups = p.bias_groups;
-#ifdef TA_EXP_ONE_TILE
-    P.k_pairs = (int)ceil_div(p.cols, kTile);
-#else
-    P.k_pairs = (int)ceil_div(p.cols, 2 * kTile);
-#endif
+    P.k_pairs = (int)ceil_div(p.cols, kTilesPerCta * kTile);
     P.q_steps = (int)ceil_div(p.cols, kStep);
     P.scale = p.scale;
     const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.k_pairs);
