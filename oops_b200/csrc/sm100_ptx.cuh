@@ -133,6 +133,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// 16-byte chunk `c` of a 128-byte row in a 128-byte-swizzled tile.  The hardware stores chunk c of row r at chunk
+// c ^ (r & 7); `row_x` is the (128-byte aligned) row address plus the thread's own term ((r & 7) ^ c0) << 4, so that
+// the chunk c0 + c (c < 8, c0 a multiple of the unrolled range) costs one XOR with an immediate.
+__device__ __forceinline__ const uint8_t* swizzled_chunk(const uint8_t* row_x, int c) {
+  return reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(row_x) ^ uintptr_t(c << 4));
+}
+
 // ---- loads that stay where they are written ---------------------------------------------------------
 // A prefetch of next step's operand only hides latency if the load issues before this step's work.  The compiler
 // may sink an ordinary load to its first use (it does when registers are tight); a volatile asm load keeps its

@@ -379,6 +379,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       };
       // S = Q K^T and dP = dO V^T of step j for query tile w (all operands K-major, 64-byte swizzle)
       auto issue_scores = [&](int j, int w) {
+        // the bias tile of the step has landed before the scores are announced: the warpgroups do not wait for it
+        if (HAS_BIAS && !mbar_wait(bar(DqSmem::bias_full + w * 2 + (j & 1)), (j >> 1) & 1, abort_flag)) return;
         const uint32_t kv = smem_base + DqSmem::kv + (j % kRing) * 2 * kSmallTile;
         const uint32_t s_t = tmem_base + w * kTileCols;
         const uint64_t qdesc = smem_desc(smem_base + DqSmem::q + w * kBigTile, 16, 512, kSwizzle64B);
@@ -498,18 +500,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       mbar_arrive_warp(bar(DqSmem::sd_free + w));
       TB_CLOCK(qk2);
       const int slot = w * 2 + (j & 1);
-      if (HAS_BIAS) {
-        ok = mbar_wait(bar(DqSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-      }
       TB_CLOCK(qk3);
-      const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128;
+      const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128 + (((t & 7) ^ (half * 4)) << 4);
       uint32_t packed[16];
       const int key0 = j * kStep + half * 32;
 #pragma unroll
       for (int i8 = 0; i8 < 4; ++i8) {
         f32x2 p2[4], ds2[4];
-        score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + i8) ^ (t & 7)) << 4), c2, log2e2, nl2,
+        score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, swizzled_chunk(bias_row, i8), c2, log2e2, nl2,
                                  nd2, p2, ds2);
         if (my_bits != 0xffffffffu) {
 #pragma unroll
@@ -715,6 +713,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
       bool ok = true;
       // S^T[128 k x 64 q] = K Q^T and dP^T = V dO^T of step j for key tile w
       auto issue_scores = [&](int j, int w) {
+        // the bias tile of the step has landed before the scores are announced: the warpgroups do not wait for it
+        if (HAS_BIAS && !mbar_wait(bar(DkvSmem::bias_full + w * 2 + (j & 1)), (j >> 1) & 1, abort_flag)) return;
         const uint32_t qd = smem_base + DkvSmem::qd + (j % kRing) * 2 * kSmallTile;
         const uint32_t st_t = tmem_base + w * kTileCols;
         const uint64_t kdesc = smem_desc(smem_base + DkvSmem::k + w * kBigTile, 16, 512, kSwizzle64B);
@@ -842,12 +842,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
       tc_fence_after_sync();
       const int slot = w * 2 + (j & 1);
       TB_CLOCK(tk3);
-      if (HAS_BIAS) {
-        ok = mbar_wait(bar(DkvSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-      }
       TB_CLOCK(tk4);
-      const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128;
+      const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128 + (((t & 7) ^ (half * 4)) << 4);
       uint32_t p_packed[16], ds_packed[16];
       // two rounds of 16 queries keep the live registers low; the score columns are released after the second load
 #pragma unroll
@@ -871,7 +867,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
             const f32x2 nl2[4] = {pack2(n01.x, n01.y), pack2(n01.z, n01.w), pack2(n23.x, n23.y), pack2(n23.z, n23.w)};
             const f32x2 nd2[4] = {pack2(d01.x, d01.y), pack2(d01.z, d01.w), pack2(d23.x, d23.y), pack2(d23.z, d23.w)};
             f32x2 p2[4], ds2[4];
-            score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_row + (((half * 4 + c8) ^ (t & 7)) << 4), c2, log2e2,
+            score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, swizzled_chunk(bias_row, c8), c2, log2e2,
                                      nl2, nd2, p2, ds2);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
