@@ -306,31 +306,36 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
     tmem_relinquish();
     tc_fence_before_sync();
   }
-  uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::drop_flags);
-  if (has_bits && warp < kElemWarps) {
-    const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
-    bool dropped_any = false;
-    for (int word = warp; word < KS * 2; word += kElemWarps) {
-      const int key = word * 32 + lane;
-      bool keep = key < P.cols;
-      if (keep && has_mask) {
-        keep = mask_row[int64_t(key) * P.m_sc] != 0;
-        dropped_any |= !keep;
-      }
-      const uint32_t bits = __ballot_sync(0xffffffffu, keep);
-      if (lane == 0) keep_words[word] = bits;
-    }
-    dropped_any = __any_sync(0xffffffffu, dropped_any);
-    if (lane == 0) drop_flags[warp] = dropped_any ? 1u : 0u;
-  }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // Key rows only need the sign-off handshake when the mask really drops a key of this row.
+  // The keep-bit table is built after the CTA-wide barrier, by the element-wise warps, while the producer's first
+  // copies are already in flight; only its users (those warps and the issuing warps) meet at a named barrier.
+  uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::drop_flags);
   bool signoff = false;
-  if (has_mask) {
+  if (has_bits && warp != kProducerWarp) {
+    if (warp < kElemWarps) {
+      const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+      bool dropped_any = false;
+      for (int word = warp; word < KS * 2; word += kElemWarps) {
+        const int key = word * 32 + lane;
+        bool keep = key < P.cols;
+        if (keep && has_mask) {
+          keep = mask_row[int64_t(key) * P.m_sc] != 0;
+          dropped_any |= !keep;
+        }
+        const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) keep_words[word] = bits;
+      }
+      dropped_any = __any_sync(0xffffffffu, dropped_any);
+      if (lane == 0) drop_flags[warp] = dropped_any ? 1u : 0u;
+    }
+    named_barrier_sync(1, kThreads - 32);
+    // Key rows only need the sign-off handshake when the mask really drops a key of this row.
+    if (has_mask) {
 #pragma unroll
-    for (int i = 0; i < kElemWarps; ++i) signoff |= drop_flags[i] != 0;
+      for (int i = 0; i < kElemWarps; ++i) signoff |= drop_flags[i] != 0;
+    }
   }
 
   if (warp == kProducerWarp) {
