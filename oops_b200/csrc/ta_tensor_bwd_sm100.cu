@@ -5,19 +5,21 @@
 // With P = exp(S - lse), dP = dO V^T, dS = P o (dP - delta) (kernel.py:499-564):
 //
 //   delta kernel     delta[q] = sum_d O[q,d] dO[q,d]                           (memory bound)
-//   dQ kernel        CTA = (batch,row,head, 2 query tiles), streams 64-key steps:
+//   dQ kernel        CTA = (batch,row,head, one 128-query tile), streams 64-key steps:
 //                    S = Q K^T, dP = dO V^T -> dS (16-bit, back into tensor memory) -> dQ += dS K.
 //                    A per-row bias gradient is dS itself and is stored from here.
-//   dK/dV kernel     CTA = (batch,row,head, 2 key tiles), streams 64-query steps, transposed:
+//   dK/dV kernel     CTA = (batch,row,head, one 128-key tile), streams 64-query steps, transposed:
 //                    S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T (tensor memory) -> dV += P^T dO, dK += dS^T Q.
 //                    It reads a transposed copy of the bias so that a thread (= one key) reads a bias row.
 //   shared-bias      CTA = (row part, batch, head, query tile, key tile) loops over its rows:
-//   gradient         S, dP -> dS accumulated in f32 registers over the rows (two warpgroups split the
+//   gradient         S, dP -> dS accumulated in f32 registers over the rows (four warpgroups split the
 //                    128 keys), one f32 partial plane per part; a last kernel adds the parts in a fixed
 //                    order (no atomics, bitwise reproducible).
 //
 // All kernels share the forward kernel's structure: one TMA producer thread, one MMA-issuing thread,
-// two warpgroups of 128 threads that own one tensor-memory lane (= one query or key) each.
+// warpgroups of 128 threads that own one tensor-memory lane (= one query or key) each.  The dQ and dK/dV
+// kernels keep 256 tensor-memory columns and under 113 KB of shared memory, so two CTAs share an SM: their
+// MMA threads run independently and one CTA's prologue and epilogue overlap the other's steps.
 #include "ta_tensor_common.cuh"
 
 namespace oops_ta {
