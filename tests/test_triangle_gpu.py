@@ -593,7 +593,8 @@ def test_config3_training_shape(cuda):
 
 
 def test_config4_ending_node_ragged(cuda):
-    """BASELINE config 4 at reduced lengths for the oracle (full lengths run in the benchmark):
+    """BASELINE config 4 at reduced lengths, where the oracle covers every row and every gradient (the full lengths
+    are covered by test_config4_full_lengths):
     ending-node ragged batch, bf16, forward+backward, shared bias, all-valid masks."""
     case = nested_case(torch.bfloat16, cuda, lengths=(160, 100), heads=4, dim=32, bias_kind="shared",
                        transposed=True, seed=4)
@@ -606,6 +607,74 @@ def test_config4_ending_node_ragged(cuda):
     grads = torch.autograd.grad(values, [leaves[n] for n in ("q", "k", "v", "bias")], upstream.to(cuda))
     for name, grad in zip(("q", "k", "v", "bias"), grads):
         assert_within(grad, want[name], 2e-2 * max(1.0, float(want[name].abs().max())), f"d{name}")
+
+
+def test_config5_full_size_properties(cuda):
+    """BASELINE config 5 at its full size (bf16 forward+backward, N=2048, all-ones mask).  The f32 oracle checks
+    out/dq/dk/dv on a seeded sample of pair rows (rows are independent).  The shared-bias gradient, a sum over all
+    2048 rows, is checked through size-independent properties: additivity over a split of the rows, bitwise
+    repeatability, and agreement with the f32-accumulating layout-agnostic kernels on a quarter of the rows."""
+    n = 2048
+    q, k, v, bias, mask, upstream = baseline_inputs(n, torch.bfloat16, seed=11)
+    dev = [t.to(cuda) for t in (q, k, v, bias)]
+    mask_d, up_d = mask.to(cuda), upstream.to(cuda)
+    leaves = [t.detach().requires_grad_(True) for t in dev]
+    out = triangle_attention(leaves[0], leaves[1], leaves[2], mask_d, leaves[3])
+    dq, dk, dv, db = torch.autograd.grad(out, leaves, up_d)
+    rows = torch.randperm(n, generator=torch.Generator().manual_seed(2))[:3].sort().values
+    want = oracle.forward_backward(q[:, rows], k[:, rows], v[:, rows], mask[:, rows], bias, upstream[:, rows])
+    assert_within(out[:, rows], want[0], 2e-2, "out")
+    for name, got, ref in (("dq", dq, want[1]), ("dk", dk, want[2]), ("dv", dv, want[3])):
+        assert_within(got[:, rows], ref, 2e-2 * max(1.0, float(ref.abs().max())), name)
+    assert torch.isfinite(db.float()).all()
+
+    def bias_grad(rows_slice):
+        b = dev[3].detach().requires_grad_(True)
+        o = triangle_attention(dev[0][:, rows_slice], dev[1][:, rows_slice], dev[2][:, rows_slice], mask_d[:, rows_slice], b)
+        return torch.autograd.grad(o, b, up_d[:, rows_slice])[0]
+
+    tolerance = 2e-2 * max(1.0, float(db.float().abs().max()))
+    halves = bias_grad(slice(0, n // 2)).float() + bias_grad(slice(n // 2, n)).float()
+    assert_within(db.float(), halves, tolerance, "dbias additivity over rows")
+    assert torch.equal(bias_grad(slice(0, n // 2)), bias_grad(slice(0, n // 2))), "dbias must be bitwise repeatable"
+    quarter = slice(0, n // 4)
+    with layout_agnostic_kernels():
+        reference_quarter = bias_grad(quarter)
+    assert_within(bias_grad(quarter), reference_quarter, 2e-2 * max(1.0, float(reference_quarter.float().abs().max())),
+                  "dbias vs f32-accumulating kernels")
+
+
+def test_config4_full_lengths(cuda):
+    """BASELINE config 4 at its full lengths (ending-node ragged batch, lengths 1024 and 700, bf16, shared bias).
+    The packed call must agree bit for bit with one dense ending-node call per sample (same kernels, same tiles),
+    and a seeded sample of logical rows of each sample is checked against the f32 oracle."""
+    lengths, heads, dim = (1024, 700), 4, 32
+    gen = torch.Generator().manual_seed(6)
+    stored = {name: [(torch.randn(L, L, heads, dim, generator=gen) * 0.5).to(torch.bfloat16) for L in lengths] for name in "qkv"}
+    biases = [torch.randn(1, heads, L, L, generator=gen).to(torch.bfloat16) for L in lengths]
+    nested = {name: NestedTensor(stored[name], ragged_dims=(0, 1)) for name in "qkv"}
+    packed = {name: nested[name].packed_like(nested[name].concat.to(cuda)).transpose(-4, -3) for name in "qkv"}
+    bias_template = NestedTensor(biases, ragged_dims=(2, 3))
+    packed_bias = bias_template.packed_like(bias_template.concat.to(cuda)).transpose(-2, -1)
+    with torch.no_grad():
+        values = triangle_attention(packed["q"], packed["k"], packed["v"], None, packed_bias).concat
+    at = 0
+    for i, L in enumerate(lengths):
+        block = values[at : at + L * L].reshape(L, L, heads, dim)  # stored order of sample i
+        at += L * L
+        # the logical sample is the pair-axes transpose of the stored element (ending node)
+        logical = {name: stored[name][i].transpose(0, 1) for name in "qkv"}
+        logical_bias = biases[i].transpose(-2, -1)
+        with torch.no_grad():
+            dense = triangle_attention(
+                *(logical[name].to(cuda)[None] for name in "qkv"), None, logical_bias.to(cuda)[None]
+            )[0]
+        assert torch.equal(block.transpose(0, 1), dense), f"sample {i}: packed and dense calls differ"
+        rows = torch.randperm(L, generator=torch.Generator().manual_seed(7 + i))[:3].sort().values
+        want = oracle.forward(
+            logical["q"][None][:, rows], logical["k"][None][:, rows], logical["v"][None][:, rows], None, logical_bias[None]
+        )
+        assert_within(dense[None][:, rows], want, 2e-2, f"sample {i} out")
 
 
 def test_padded_dense_equals_ragged(cuda):
