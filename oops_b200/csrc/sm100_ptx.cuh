@@ -42,44 +42,6 @@ __device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
 constexpr uint32_t kSuspendHintNs = 20000;  // 20 us per probe; the bounded wait below re-probes until its own limit
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
-#ifdef TA_SPIN_TEST_WAIT
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-#endif
-#ifdef TA_EXP_HOT_ISSUERS
-  if (threadIdx.x >= blockDim.x - 64) {  // the TMA and MMA issuing warps probe without parking
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-  }
-#endif
-#ifdef TA_EXP_NO_HINT
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-#endif
   // The suspend-time hint lets the hardware park the warp until the phase completes (or the hint expires)
   // instead of returning at once, so a waiting warp does not burn issue slots of the warps that compute.
   asm volatile(

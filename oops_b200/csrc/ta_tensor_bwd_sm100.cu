@@ -31,7 +31,11 @@ constexpr int kTilesPerCta = 1;                          // dQ and dK/dV kernels
 constexpr int kElemWarps = 8 * kTilesPerCta;             // two warpgroups per tile
 constexpr int kThreads = (kElemWarps + (kTilesPerCta == 2 ? 3 : 2)) * 32;
 constexpr int kCtasPerSm = kTilesPerCta == 2 ? 1 : 2;
-constexpr int kDbThreads = 576;                          // shared-bias kernel: 16 + 2 warps
+constexpr int kDbKeys = 64;                              // shared-bias kernel: keys of a CTA's tile (64 or 128)
+constexpr int kDbElemWarps = 4 * (kDbKeys / 32);         // one warpgroup per 32 keys
+constexpr int kDbThreads = (kDbElemWarps + 2) * 32;
+constexpr int kDbCtasPerSm = kDbKeys == 64 ? 2 : 1;
+constexpr int kDbKvTile = kDbKeys * kHeadDim * 2;        // K or V rows of the tile
 constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
 constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
 constexpr int kSmallTile = kStep * kHeadDim * 2;        // 4 KiB: 64 x 32 tile
@@ -143,7 +147,7 @@ __device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
 // between two warpgroups that address the same tensor-memory lanes (warp % 4 selects the lanes).
 
 constexpr int kProducerWarp = kElemWarps, kMmaWarp = kElemWarps + 1, kAccWarp = kElemWarps + 2;
-constexpr int kDbProducerWarp = 16, kDbMmaWarp = 17;
+constexpr int kDbProducerWarp = kDbElemWarps, kDbMmaWarp = kDbElemWarps + 1;
 
 #ifdef TA_PROFILE_WAITS
 // dK/dV kernel, clocks summed over warpgroups (thread 0 of each): 0 sd_full, 1 bias_full, 2 pds_done, 3 stats+named barrier,
@@ -175,21 +179,12 @@ __device__ __forceinline__ void score_grad8(const uint32_t* sraw, const uint32_t
   for (int i = 0; i < 4; ++i) {
     const f32x2 s2 = pack2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1]));
     const f32x2 d2 = pack2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1]));
-#ifdef TA_EXP_BWD_NOMATH
-    p2[i] = s2;
-    ds2[i] = d2;
-#else
     const f32x2 offset = HAS_BIAS ? fma2(Half2<T>::widen(bw[i]), log2e2, nl2[i]) : nl2[i];
     float lo, hi;
     unpack2(fma2(s2, c2, offset), lo, hi);
-#ifdef TA_EXP_NOEXP
-    const f32x2 p = pack2(lo, hi);
-#else
     const f32x2 p = pack2(ex2(lo), ex2(hi));
-#endif
     p2[i] = p;
     ds2[i] = mul2(p, add2(d2, nd2[i]));
-#endif
   }
 }
 
@@ -946,9 +941,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
 
 constexpr int kDbRing = 3;
 struct DbSmem {
-  static constexpr int bias = 0;                                // 128 x 128 (two 64-key boxes)
-  static constexpr int ring = bias + 2 * kBiasStep;             // [kDbRing] Q | dO | K | V, 8 KiB each
-  static constexpr int bars = ring + kDbRing * 4 * kBigTile;
+  static constexpr int bias = 0;                                // 128 queries x kDbKeys (64-key boxes)
+  static constexpr int ring = bias + (kDbKeys / 64) * kBiasStep;      // [kDbRing] Q | dO (8 KiB each) | K | V
+  static constexpr int stage = 2 * kBigTile + 2 * kDbKvTile;
+  static constexpr int bars = ring + kDbRing * stage;
   static constexpr int bias_full = 0;
   static constexpr int row_full = 1;                     // [kDbRing]
   static constexpr int row_empty = row_full + kDbRing;   // [kDbRing]
@@ -969,12 +965,12 @@ struct DbParams {
   const uint8_t* mask;
   int64_t m_sb, m_sr, m_sc;
   int batch, rows, cols, heads;
-  int tiles, num_parts, rows_per_part;
+  int tiles, k_tiles, num_parts, rows_per_part;
   float scale;
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
+__global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -985,8 +981,8 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
-  const int kt = idx % P.tiles;
-  idx /= P.tiles;
+  const int kt = idx % P.k_tiles;
+  idx /= P.k_tiles;
   const int qt = idx % P.tiles;
   idx /= P.tiles;
   const int h = idx % P.heads;
@@ -1007,12 +1003,12 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DbSmem::sd_full + i), 1);
-      mbar_init(bar(DbSmem::sd_free + i), 16);
+      mbar_init(bar(DbSmem::sd_free + i), kDbElemWarps);
     }
     fence_barrier_init();
   }
   if (warp == kDbMmaWarp) {
-    tmem_alloc(smem_base + DbSmem::tmem_slot, 512);
+    tmem_alloc(smem_base + DbSmem::tmem_slot, 4 * kDbKeys);
     tmem_relinquish();
     tc_fence_before_sync();
   }
@@ -1023,25 +1019,26 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
   if (warp == kDbProducerWarp) {
     if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(bar(DbSmem::bias_full), 2 * kBiasStep);
-      tma_load_5d(smem_base + DbSmem::bias, &P.map_bias, bar(DbSmem::bias_full), kt * kTile, qt * kTile, h, 0, b);
-      tma_load_5d(smem_base + DbSmem::bias + kBiasStep, &P.map_bias, bar(DbSmem::bias_full), kt * kTile + 64, qt * kTile, h, 0, b);
+      mbar_expect_tx(bar(DbSmem::bias_full), (kDbKeys / 64) * kBiasStep);
+      for (int box = 0; box < kDbKeys / 64; ++box)
+        tma_load_5d(smem_base + DbSmem::bias + box * kBiasStep, &P.map_bias, bar(DbSmem::bias_full), kt * kDbKeys + box * 64,
+                    qt * kTile, h, 0, b);
       for (int i = 0; i < n_rows && ok; ++i) {
         const int st = i % kDbRing, round = i / kDbRing, r = row_lo + i;
         if (i >= kDbRing) ok = mbar_wait(bar(DbSmem::row_empty + st), (round - 1) & 1, abort_flag);
         if (!ok) break;
-        mbar_expect_tx(bar(DbSmem::row_full + st), 4 * kBigTile);
-        const uint32_t dst = smem_base + DbSmem::ring + st * 4 * kBigTile;
+        mbar_expect_tx(bar(DbSmem::row_full + st), DbSmem::stage);
+        const uint32_t dst = smem_base + DbSmem::ring + st * DbSmem::stage;
         tma_load_5d(dst, &P.map_q, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
         tma_load_5d(dst + kBigTile, &P.map_dout, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
-        tma_load_5d(dst + 2 * kBigTile, &P.map_k, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
-        tma_load_5d(dst + 3 * kBigTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
+        tma_load_5d(dst + 2 * kBigTile, &P.map_k, bar(DbSmem::row_full + st), 0, h, kt * kDbKeys, r, b);
+        tma_load_5d(dst + 2 * kBigTile + kDbKvTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kDbKeys, r, b);
       }
     }
   } else if (warp == kDbMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t fmt = Half2<T>::kFormat;
-      constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kDbKeys);
       bool ok = true;
       for (int i = 0; i < n_rows && ok; ++i) {
         const int st = i % kDbRing, buf = i & 1;
@@ -1049,29 +1046,29 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
         if (ok && i >= 2) ok = mbar_wait(bar(DbSmem::sd_free + buf), ((i >> 1) - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t base = smem_base + DbSmem::ring + st * 4 * kBigTile;
+        const uint32_t base = smem_base + DbSmem::ring + st * DbSmem::stage;
         const uint64_t qdesc = smem_desc(base, 16, 512, kSwizzle64B);
         const uint64_t ddesc = smem_desc(base + kBigTile, 16, 512, kSwizzle64B);
         const uint64_t kdesc = smem_desc(base + 2 * kBigTile, 16, 512, kSwizzle64B);
-        const uint64_t vdesc = smem_desc(base + 3 * kBigTile, 16, 512, kSwizzle64B);
-        const uint32_t s_t = tmem_base + buf * 2 * kTile;
+        const uint64_t vdesc = smem_desc(base + 2 * kBigTile + kDbKvTile, 16, 512, kSwizzle64B);
+        const uint32_t s_t = tmem_base + buf * 2 * kDbKeys;
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          mma_ss(s_t + kTile, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+          mma_ss(s_t + kDbKeys, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
         mma_commit(bar(DbSmem::sd_full + buf));
         mma_commit(bar(DbSmem::row_empty + st));
       }
     }
-  } else if (warp < 16) {
-    const int wg = warp >> 2;  // key quarter: 32 keys
+  } else if (warp < kDbElemWarps) {
+    const int wg = warp >> 2;  // 32 of the tile's keys
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
     const int q_index = qt * kTile + t;
     const bool q_valid = q_index < P.cols;
-    const int key_base = kt * kTile + wg * 32;
+    const int key_base = kt * kDbKeys + wg * 32;
     const float scale = P.scale;
     f32x2 acc2[16];
 #pragma unroll
@@ -1116,14 +1113,14 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
+      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kDbKeys + wg * 32;
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(-delta, -delta);
       const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
 #pragma unroll
       for (int round = 0; round < 2; ++round) {
         uint32_t sraw[16], draw[16];
         tmem_ld16(s_t + round * 16, sraw);
-        tmem_ld16(s_t + kTile + round * 16, draw);
+        tmem_ld16(s_t + kDbKeys + round * 16, draw);
         tmem_wait_ld();
         if (round == 1) {
           tc_fence_before_sync();
@@ -1160,7 +1157,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       }
     }
   }
-  teardown(abort_flag, tmem_base, kDbMmaWarp);
+  teardown(abort_flag, tmem_base, kDbMmaWarp, 4 * kDbKeys);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1172,9 +1169,8 @@ uint64_t align256(uint64_t v) { return (v + 255) & ~uint64_t(255); }
 int64_t padded_cols(const oops_ta_problem& p) { return (int64_t(p.cols) + 7) & ~int64_t(7); }
 
 int bias_parts(const oops_ta_problem& p) {
-  const int64_t tiles = ceil_div(p.cols, kTile);
-  const int64_t ctas = int64_t(p.batch) * p.heads * tiles * tiles;
-  int64_t parts = ceil_div(4 * 148, ctas);
+  const int64_t ctas = int64_t(p.batch) * p.heads * ceil_div(p.cols, kTile) * ceil_div(p.cols, kDbKeys);
+  int64_t parts = ceil_div(4 * 148 * kDbCtasPerSm, ctas);
   parts = std::max<int64_t>(1, std::min<int64_t>(parts, std::min<int64_t>(16, p.rows)));
   return (int)parts;
 }
@@ -1326,8 +1322,8 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     DbParams P{};
     status = encode_pair(&P.map_q, p, p.q, kTile, "query");
     if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
-    if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
-    if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
+    if (!status) status = encode_pair(&P.map_k, p, p.k, kDbKeys, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kDbKeys, "value");
     if (!status) status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
     if (status) return status;
     P.parts = reinterpret_cast<float*>(base + layout.parts);
@@ -1342,10 +1338,11 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.tiles = (int)ceil_div(p.cols, kTile);
+    P.k_tiles = (int)ceil_div(p.cols, kDbKeys);
     P.num_parts = bias_parts(p);
     P.rows_per_part = (int)ceil_div(p.rows, P.num_parts);
     P.scale = p.scale;
-    const unsigned grid = (unsigned)(int64_t(P.num_parts) * p.batch * p.heads * P.tiles * P.tiles);
+    const unsigned grid = (unsigned)(int64_t(P.num_parts) * p.batch * p.heads * P.tiles * P.k_tiles);
     auto kernel = ta_bwd_dbias_kernel<T>;
     status = reserve_smem(kernel, kDbSmemBytes);
     if (status) return status;

@@ -59,14 +59,8 @@ struct FwdSmem {
   static constexpr int keep = drop_flags + 32;         // [kMaxKeepWords] u32
   static constexpr int total = keep + kMaxKeepWords * 4;
 };
-#ifdef TA_EXP_ONE_CTA
-constexpr int kFwdSmemBytes = FwdSmem::total + 1024 + 8192;
-#else
 constexpr int kFwdSmemBytes = FwdSmem::total + 1024;  // slack to align the base to 1 KiB
-#endif
-#ifndef TA_EXP_ONE_CTA
 static_assert(kFwdSmemBytes <= 113 * 1024, "two forward CTAs must fit in one SM's shared memory");
-#endif
 
 struct FwdParams {
   CUtensorMap map_q, map_k, map_v, map_bias;
@@ -334,20 +328,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       const long long c1 = clock64();
 #endif
 
-#ifdef TA_EXP_SKIP_MATH
-      uint32_t packed[kKeys / 2];
-#pragma unroll
-      for (int i = 0; i < kKeys / 2; ++i) packed[i] = (__float_as_uint(x[i].x) >> 17) & 0x3f003f00u;
-      const bool raise = false;
-      const float alpha = 1.f;
-      l_run = 1.f;
-      if (HAS_BIAS) {
-        const int slot = w * 2 + (j & 1);
-        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag TA_WAIT_ARG(wbias));
-        if (!ok) break;
-        mbar_arrive_warp(bar(FwdSmem::bias_empty + slot));
-      }
-#else
       if (HAS_BIAS) {
         const int slot = w * 2 + (j & 1);
         ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag TA_WAIT_ARG(wbias));
@@ -406,18 +386,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       for (int i = 0; i < kKeys / 2; ++i) {
         float lo, hi;
         unpack2(fma2(x[i], log2e2, shift2), lo, hi);
-#ifdef TA_EXP_NOEXP
-        const float p0 = lo, p1 = hi;
-#else
         const float p0 = ex2(lo), p1 = ex2(hi);
-#endif
         totals[i & 3] = add2(totals[i & 3], pack2(p0, p1));
         packed[i] = Half2<T>::pack(p0, p1);
       }
       float t_lo, t_hi;
       unpack2(add2(add2(totals[0], totals[1]), add2(totals[2], totals[3])), t_lo, t_hi);
       l_run = l_run * alpha + (t_lo + t_hi);
-#endif  // TA_EXP_SKIP_MATH
 #ifdef TA_PROFILE_WAITS
       const long long c2 = clock64();
 #endif
