@@ -69,6 +69,10 @@ typedef enum oops_ta_status {
                                          the reference's "ieee"/3xTF32 mode promises
                                          (oops/runtime/dispatch.py:260-328)           */
 
+#define OOPS_TA_FLAG_SPLIT_REVERSE 4u /* reverse pass: take the separate dQ and dK/dV
+                                         kernels even where the single-pass kernel that
+                                         produces all three applies (testing)           */
+
 typedef struct oops_ta_pair {
   void* ptr;
   int64_t sb, sr, sc, sh; /* element strides of batch, row, column, head */

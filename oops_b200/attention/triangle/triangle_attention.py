@@ -90,6 +90,7 @@ def _describe(tensor: Optional[Tensor]) -> Optional[str]:
 
 
 _FORCE_GENERIC = False
+_SPLIT_REVERSE = False
 
 
 @contextmanager
@@ -104,10 +105,22 @@ def layout_agnostic_kernels(enabled: bool = True):
         _FORCE_GENERIC = previous
 
 
+@contextmanager
+def separate_reverse_kernels(enabled: bool = True):
+    """Route the reverse pass of calls inside the block to the separate dQ and dK/dV kernels even where the
+    single-pass kernel applies (used to test both on the same inputs)."""
+    global _SPLIT_REVERSE
+    previous, _SPLIT_REVERSE = _SPLIT_REVERSE, enabled
+    try:
+        yield
+    finally:
+        _SPLIT_REVERSE = previous
+
+
 def _flags() -> int:
     # The f32 kernels use full-precision products in every mode, which satisfies both the
     # "ieee" and the relaxed "tf32" setting of torch.backends.cuda.matmul.fp32_precision.
-    return cabi.FLAG_FORCE_GENERIC if _FORCE_GENERIC else 0
+    return (cabi.FLAG_FORCE_GENERIC if _FORCE_GENERIC else 0) | (cabi.FLAG_SPLIT_REVERSE if _SPLIT_REVERSE else 0)
 
 
 def _require_bool_mask(mask: Optional[Tensor]) -> None:

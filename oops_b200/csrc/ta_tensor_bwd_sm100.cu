@@ -936,6 +936,420 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
 }
 
 // ---------------------------------------------------------------------------------------------
+// fused dQ / dK / dV kernel: one pass over the score tiles of a pair row
+// ---------------------------------------------------------------------------------------------
+// CTA = (batch, row, head, group of up to 6 query tiles).  For every key tile and every query tile of the group:
+// S = Q K^T and dP = dO V^T (128 x 128, tensor memory) -> the four warpgroups (a thread owns a query, a warpgroup
+// 32 of the 128 keys) compute P and dS once and write them, 16-bit, into two shared-memory images whose rows
+// are queries and whose 128-byte-swizzled columns are keys.  The tensor core reads those images three ways:
+// dV += P^T dO and dK += dS^T Q take them as MN-major A operands (M = keys), dQ += dS K as a K-major A operand
+// (M = queries).  dQ of all query tiles of the group, dK and dV of the current key tile stay in tensor memory:
+// S 128 | dP 128 | dK 32 | dV 32 | dQ 6 x 32 = 512 columns.  One `ex2` per logit and five products, where the
+// separate dQ and dK/dV kernels spend two and seven.  With more than one group per row (more than 768 columns)
+// every group leaves f32 partial planes of dK and dV that a last kernel adds in a fixed order.
+
+constexpr int kFMaxQTiles = 6;
+constexpr int kFThreads = 608;  // 16 element-wise warps, TMA producer, score issuer, accumulation issuer
+constexpr int kFProducerWarp = 16, kFScoreWarp = 17, kFAccWarp = 18;
+constexpr int kFImage = 2 * 16384;       // P or dS of a step: two 64-key halves of 128 rows x 128 bytes
+constexpr int kFBias = 2 * kBiasStep;    // 128 x 128 bias tile as two 64-key boxes
+
+struct FSmem {
+  static constexpr int q = 0;                          // [3] 128 x 32 (a slot is held until the step's dK product ends)
+  static constexpr int dout = q + 3 * kBigTile;        // [3]
+  static constexpr int k = dout + 3 * kBigTile;        // [2]
+  static constexpr int v = k + 2 * kBigTile;           // [2]
+  static constexpr int ps = v + 2 * kBigTile;          // P image
+  static constexpr int dss = ps + kFImage;             // dS image
+  static constexpr int bias = dss + kFImage;           // [2]
+  static constexpr int bars = bias + 2 * kFBias;
+  static constexpr int qd_full = 0;                    // [3]
+  static constexpr int qd_empty = qd_full + 3;         // [3]
+  static constexpr int kv_full = qd_empty + 3;         // [2]
+  static constexpr int kv_empty = kv_full + 2;         // [2]
+  static constexpr int k_ready = kv_empty + 2;         // [2] dropped keys' rows cleared (only with a dropping mask)
+  static constexpr int bias_full = k_ready + 2;        // [2]
+  static constexpr int bias_empty = bias_full + 2;     // [2]
+  static constexpr int sd_full = bias_empty + 2;       // S and dP of a step are in tensor memory
+  static constexpr int sd_free = sd_full + 1;          // all warps have read them
+  static constexpr int pds_full = sd_free + 1;         // the P and dS images are written
+  static constexpr int pds_done = pds_full + 1;        // the three accumulating products have consumed them
+  static constexpr int dkv_free = pds_done + 1;        // dK and dV of a finished key tile have been read out
+  static constexpr int num_bars = dkv_free + 1;
+  static constexpr int tmem_slot = bars + num_bars * 8;
+  static constexpr int abort_flag = tmem_slot + 4;
+  static constexpr int drop_flags = abort_flag + 4;    // [16]
+  static constexpr int keep = drop_flags + 64;
+  static constexpr int total = keep + kMaxKeepWords * 4;
+};
+constexpr int kFSmemBytes = FSmem::total + 1024;
+
+struct FParams {
+  CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
+  oops_ta_pair dq, dk, dv;
+  float* dk_parts;  // [groups][batch][rows][cols][heads][32] f32, used when groups > 1
+  float* dv_parts;
+  const float* lse;
+  const float* delta;
+  const uint8_t* mask;
+  int64_t m_sb, m_sr, m_sc;
+  int batch, rows, cols, heads, bias_groups;
+  int q_tiles, k_tiles, groups, tiles_per_group;
+  int write_dq, write_dk, write_dv;
+  float scale;
+};
+
+template <typename T, bool HAS_BIAS>
+__global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid_constant__ FParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + FSmem::abort_flag);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + FSmem::tmem_slot);
+  uint32_t* keep_words = reinterpret_cast<uint32_t*>(smem_gen + FSmem::keep);
+  auto bar = [&](int index) -> uint32_t { return smem_base + FSmem::bars + index * 8; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (device_failed()) return;
+  int idx = blockIdx.x;
+  const int group = idx % P.groups;
+  idx /= P.groups;
+  const int h = idx % P.heads;
+  idx /= P.heads;
+  const int r = idx % P.rows;
+  const int b = idx / P.rows;
+  const int qt0 = group * P.tiles_per_group;
+  const int nq = min(P.tiles_per_group, P.q_tiles - qt0);
+  const int KT = P.k_tiles;
+  const int steps = KT * nq;  // step s: key tile s / nq, query tile qt0 + s % nq
+  const int g = P.bias_groups == 1 ? 0 : r;
+  const bool has_mask = P.mask != nullptr;
+  const bool has_bits = has_mask || (P.cols % kTile) != 0;
+  // tensor-memory columns
+  constexpr int kSCol = 0, kDpCol = 128, kDkCol = 256, kDvCol = 288, kDqCol = 320;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(bar(FSmem::qd_full + i), 1);
+      mbar_init(bar(FSmem::qd_empty + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(FSmem::kv_full + i), 1);
+      mbar_init(bar(FSmem::kv_empty + i), 1);
+      mbar_init(bar(FSmem::k_ready + i), 4);
+      mbar_init(bar(FSmem::bias_full + i), 1);
+      mbar_init(bar(FSmem::bias_empty + i), 16);
+    }
+    mbar_init(bar(FSmem::sd_full), 1);
+    mbar_init(bar(FSmem::sd_free), 16);
+    mbar_init(bar(FSmem::pds_full), 16);
+    mbar_init(bar(FSmem::pds_done), 1);
+    mbar_init(bar(FSmem::dkv_free), 8);
+    fence_barrier_init();
+  }
+  if (warp == kFScoreWarp) {
+    tmem_alloc(smem_base + FSmem::tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // keep-bit table (one bit per key of this pair row), built by the element-wise warps while the first copies fly
+  uint32_t* drop_flags = reinterpret_cast<uint32_t*>(smem_gen + FSmem::drop_flags);
+  bool signoff = false;
+  if (has_bits && warp != kFProducerWarp) {
+    if (warp < 16) {
+      const uint8_t* mask_row = has_mask ? P.mask + b * P.m_sb + int64_t(r) * P.m_sr : nullptr;
+      bool dropped_any = false;
+      for (int word = warp; word < KT * 4; word += 16) {
+        const int key = word * 32 + lane;
+        bool keep = key < P.cols;
+        if (keep && has_mask) {
+          keep = mask_row[int64_t(key) * P.m_sc] != 0;
+          dropped_any |= !keep;
+        }
+        const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) keep_words[word] = bits;
+      }
+      dropped_any = __any_sync(0xffffffffu, dropped_any);
+      if (lane == 0) drop_flags[warp] = dropped_any ? 1u : 0u;
+    }
+    named_barrier_sync(1, kFThreads - 32);
+    if (has_mask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) signoff |= drop_flags[i] != 0;
+    }
+  }
+
+  if (warp == kFProducerWarp) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int s = 0; s < steps && ok; ++s) {
+        const int kt = s / nq, qt = qt0 + s % nq, slot = s & 1, qs = s % 3;
+        if (s % nq == 0) {
+          const int ks = kt & 1;
+          if (kt >= 2) ok = mbar_wait(bar(FSmem::kv_empty + ks), ((kt >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar(FSmem::kv_full + ks), 2 * kBigTile);
+          tma_load_5d(smem_base + FSmem::k + ks * kBigTile, &P.map_k, bar(FSmem::kv_full + ks), 0, h, kt * kTile, r, b);
+          tma_load_5d(smem_base + FSmem::v + ks * kBigTile, &P.map_v, bar(FSmem::kv_full + ks), 0, h, kt * kTile, r, b);
+        }
+        if (s >= 3) ok = mbar_wait(bar(FSmem::qd_empty + qs), ((s / 3) - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bar(FSmem::qd_full + qs), 2 * kBigTile);
+        tma_load_5d(smem_base + FSmem::q + qs * kBigTile, &P.map_q, bar(FSmem::qd_full + qs), 0, h, qt * kTile, r, b);
+        tma_load_5d(smem_base + FSmem::dout + qs * kBigTile, &P.map_dout, bar(FSmem::qd_full + qs), 0, h, qt * kTile, r, b);
+        if (HAS_BIAS) {
+          if (s >= 2) ok = mbar_wait(bar(FSmem::bias_empty + slot), ((s >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar(FSmem::bias_full + slot), kFBias);
+          for (int box = 0; box < 2; ++box)
+            tma_load_5d(smem_base + FSmem::bias + slot * kFBias + box * kBiasStep, &P.map_bias, bar(FSmem::bias_full + slot),
+                        kt * kTile + box * 64, qt * kTile, h, g, b);
+        }
+      }
+    }
+  } else if (warp == kFScoreWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
+      bool ok = true;
+      for (int s = 0; s < steps && ok; ++s) {
+        const int kt = s / nq, qs = s % 3, ks = kt & 1;
+        ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
+        if (ok && s % nq == 0) {
+          ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
+          if (ok && signoff) ok = mbar_wait(bar(FSmem::k_ready + ks), (kt >> 1) & 1, abort_flag);
+        }
+        if (ok && s > 0) ok = mbar_wait(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);
+        const uint64_t vdesc = smem_desc(smem_base + FSmem::v + ks * kBigTile, 16, 512, kSwizzle64B);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(tmem_base + kSCol, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          mma_ss(tmem_base + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+        mma_commit(bar(FSmem::sd_full));
+      }
+    }
+  } else if (warp == kFAccWarp) {
+    if (lane == 0) {
+      constexpr uint32_t fmt = Half2<T>::kFormat;
+      constexpr uint32_t idesc_t = instr_desc(fmt, 1, 1, kTile, kHeadDim);  // A = image^T (M = keys), B MN-major
+      constexpr uint32_t idesc_q = instr_desc(fmt, 0, 1, kTile, kHeadDim);  // A = image (M = queries), B MN-major
+      bool ok = true;
+      for (int s = 0; s < steps && ok; ++s) {
+        const int kt = s / nq, qi = s % nq, qs = s % 3, ks = kt & 1;
+        ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
+        if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
+        if (ok) ok = mbar_wait(bar(FSmem::pds_full), s & 1, abort_flag);
+        // dK and dV of the previous key tile must have been read out before they are overwritten
+        if (ok && qi == 0 && kt > 0) ok = mbar_wait(bar(FSmem::dkv_free), (kt - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss;
+        const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);     // MN-major B
+        const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);  // MN-major B
+        const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);       // MN-major B
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 128 q] dO[128 q x 32]
+          mma_ss(tmem_base + kDvCol, smem_desc(ps + kk * 2048, 16384, 1024, kSwizzle128B), ddesc + uint64_t(kk * (1024 >> 4)),
+                 idesc_t, (qi > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 128 q] Q[128 q x 32]
+          mma_ss(tmem_base + kDkCol, smem_desc(dss + kk * 2048, 16384, 1024, kSwizzle128B), qdesc + uint64_t(kk * (1024 >> 4)),
+                 idesc_t, (qi > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dQ[128 q x 32] += dS[128 q x 128 k] K[128 k x 32]
+          mma_ss(tmem_base + kDqCol + qi * kHeadDim, smem_desc(dss + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, kSwizzle128B),
+                 kdesc + uint64_t(kk * (1024 >> 4)), idesc_q, (kt > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(bar(FSmem::pds_done));
+        mma_commit(bar(FSmem::qd_empty + qs));
+        if (qi == nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
+      }
+    }
+  } else if (warp < 16) {
+    const int wg = warp >> 2;  // 32 of the step's 128 keys
+    const int t = tid & (kTile - 1);
+    const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t lanes_t = tmem_base + lane_field;
+    const float scale = P.scale;
+    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
+    const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
+    // statistics of this thread's query in the step's query tile, fetched one step ahead and left untouched till then
+    auto fetch_stats = [&](int s, float& lse_raw, float& delta_raw) {
+      lse_raw = INFINITY;
+      delta_raw = 0.f;
+      const int q = (qt0 + s % nq) * kTile + t;
+      if (s < steps && q < P.cols) {
+        lse_raw = ldg_f32_here(P.lse + stat_base + q);
+        delta_raw = ldg_f32_here(P.delta + stat_base + q);
+      }
+    };
+    // dK (warpgroup 0) and dV (warpgroup 1) of key tile kt: lanes are keys
+    auto store_key_tile = [&](int kt) {
+      if (wg > 1) return;
+      uint32_t acc[32];
+      tmem_ld32(lanes_t + (wg == 0 ? kDkCol : kDvCol), acc);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(FSmem::dkv_free));
+      const int key = kt * kTile + t;
+      if (key >= P.cols) return;
+      const bool wanted = wg == 0 ? P.write_dk != 0 : P.write_dv != 0;
+      if (!wanted) return;
+      if (P.groups > 1) {
+        float* dst = (wg == 0 ? P.dk_parts : P.dv_parts) +
+                     ((((int64_t(group) * P.batch + b) * P.rows + r) * P.cols + key) * P.heads + h) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                                           __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+      } else {
+        const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
+        T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
+        store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
+      }
+    };
+    float lse_next, delta_next;
+    fetch_stats(0, lse_next, delta_next);
+    bool ok = true;
+
+    for (int s = 0; s < steps && ok; ++s) {
+      const int kt = s / nq, qi = s % nq, slot = s & 1;
+      const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
+      fetch_stats(s + 1, lse_next, delta_next);
+      const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
+      const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
+      const uint32_t bits = has_bits ? keep_words[kt * 4 + wg] : 0xffffffffu;
+      if (signoff && qi == 0 && warp < 4) {
+        // key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory
+        const int ks = kt & 1;
+        ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
+        if (!ok) break;
+        if (((keep_words[kt * 4 + (t >> 5)] >> (t & 31)) & 1u) == 0) {
+          uint4* row = reinterpret_cast<uint4*>(smem_gen + FSmem::k + ks * kBigTile + t * 64);
+          row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive_warp(bar(FSmem::k_ready + ks));
+      }
+      ok = mbar_wait(bar(FSmem::sd_full), s & 1, abort_flag);
+      if (ok && HAS_BIAS) ok = mbar_wait(bar(FSmem::bias_full + slot), (s >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      // bias row of this query: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
+      const uint8_t* bias_row = smem_gen + FSmem::bias + slot * kFBias + (wg >> 1) * kBiasStep + t * 128 +
+                                (((t & 7) ^ ((wg & 1) * 4)) << 4);
+      uint32_t p_packed[16], ds_packed[16];
+#pragma unroll
+      for (int round = 0; round < 2; ++round) {
+        uint32_t sraw[16], draw[16];
+        tmem_ld16(lanes_t + kSCol + wg * 32 + round * 16, sraw);
+        tmem_ld16(lanes_t + kDpCol + wg * 32 + round * 16, draw);
+        tmem_wait_ld();
+        if (round == 1) {
+          tc_fence_before_sync();
+          mbar_arrive_warp(bar(FSmem::sd_free));
+        }
+#pragma unroll
+        for (int i8 = 0; i8 < 2; ++i8) {
+          const int c8 = round * 2 + i8;
+          f32x2 p2[4], ds2[4];
+          score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, swizzled_chunk(bias_row, c8), c2, log2e2, nl2, nd2, p2, ds2);
+          if (bits != 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              p2[i] = select2(p2[i], bits, c8 * 8 + 2 * i);
+              ds2[i] = select2(ds2[i], bits, c8 * 8 + 2 * i);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
+            ds_packed[c8 * 4 + i] = pack16<T>(ds2[i]);
+          }
+        }
+      }
+      if (HAS_BIAS) mbar_arrive_warp(bar(FSmem::bias_empty + slot));
+      if (s > 0) {
+        // the products of the previous step must have finished reading the two images
+        ok = mbar_wait(bar(FSmem::pds_done), (s - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // ... which also completes dK and dV of the previous key tile when this step opens a new one
+        if (qi == 0) store_key_tile(kt - 1);
+      }
+      // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
+      uint8_t* p_row = smem_gen + FSmem::ps + (wg >> 1) * 16384 + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
+      uint8_t* ds_row = p_row + kFImage;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
+            make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
+        *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(ds_row, c))) =
+            make_uint4(ds_packed[4 * c], ds_packed[4 * c + 1], ds_packed[4 * c + 2], ds_packed[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(bar(FSmem::pds_full));
+    }
+
+    if (ok) ok = mbar_wait(bar(FSmem::pds_done), (steps - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      store_key_tile(KT - 1);
+      // dQ of query tile qi is read out by warpgroup qi % 4 (lanes are queries)
+      for (int qi = wg; qi < nq; qi += 4) {
+        uint32_t acc[32];
+        tmem_ld32(lanes_t + kDqCol + qi * kHeadDim, acc);
+        tmem_wait_ld();
+        const int q_index = (qt0 + qi) * kTile + t;
+        if (q_index < P.cols && P.write_dq) {
+          T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
+          store_row32<T>(dst, acc, scale, pair_vec_ok(P.dq));
+        }
+      }
+    }
+  }
+  teardown(abort_flag, tmem_base, kFScoreWarp);
+}
+
+// Adds the f32 partial planes of dK or dV in a fixed order: one thread per (batch, row, column, head) vector of 32.
+template <typename T>
+__global__ void reduce_pair_parts_kernel(const float* parts, int groups, oops_ta_pair out, float scale, int batch, int rows,
+                                         int cols, int heads) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t vectors = int64_t(batch) * rows * cols * heads;
+  if (i >= vectors) return;
+  float total[32];
+#pragma unroll
+  for (int d = 0; d < 32; ++d) total[d] = 0.f;
+  for (int p = 0; p < groups; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(parts + (int64_t(p) * vectors + i) * 32);
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      const float4 v = src[d];
+      total[4 * d] += v.x; total[4 * d + 1] += v.y; total[4 * d + 2] += v.z; total[4 * d + 3] += v.w;
+    }
+  }
+  const int h = i % heads;
+  const int c = (i / heads) % cols;
+  const int r = (i / (int64_t(heads) * cols)) % rows;
+  const int64_t b = i / (int64_t(heads) * cols * rows);
+  uint32_t acc[32];
+#pragma unroll
+  for (int d = 0; d < 32; ++d) acc[d] = __float_as_uint(total[d]);
+  T* dst = reinterpret_cast<T*>(out.ptr) + b * out.sb + int64_t(r) * out.sr + int64_t(c) * out.sc + h * out.sh;
+  store_row32<T>(dst, acc, scale, pair_vec_ok(out));
+}
+
+// ---------------------------------------------------------------------------------------------
 // shared-bias gradient kernel
 // ---------------------------------------------------------------------------------------------
 
@@ -1175,8 +1589,17 @@ int bias_parts(const oops_ta_problem& p) {
   return (int)parts;
 }
 
+// The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient.
+bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
+  if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
+  if (g.dbias && p.bias_groups > 1) return false;
+  return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
+}
+
+int fused_groups(const oops_ta_problem& p) { return (int)ceil_div(ceil_div(p.cols, kTile), kFMaxQTiles); }
+
 struct Layout {
-  uint64_t delta, bias_t, parts, total;
+  uint64_t delta, bias_t, parts, pair_parts, total;
 };
 
 Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
@@ -1185,8 +1608,12 @@ Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
   l.delta = at;
   at += align256(uint64_t(p.batch) * p.rows * p.heads * p.cols * sizeof(float));
   l.bias_t = at;
-  if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr))
+  const bool fused = fused_applies(p, g);
+  if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr) && !fused)
     at += align256(uint64_t(p.batch) * p.bias_groups * p.heads * p.cols * padded_cols(p) * 2);
+  l.pair_parts = at;  // f32 partial planes of dK, then of dV, one per query group
+  if (fused && fused_groups(p) > 1)
+    at += 2 * align256(uint64_t(fused_groups(p)) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
   l.parts = at;
   if (g.dbias && p.bias_groups == 1)
     at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
@@ -1232,8 +1659,73 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     if (status) return status;
   }
 
-  CUtensorMap map_q128, map_d128, map_k128, map_v128;
-  if (g.dq.ptr || row_bias_grad) {
+  const bool fused = fused_applies(p, g);
+  if (fused) {
+    FParams P{};
+    status = encode_pair(&P.map_q, p, p.q, kTile, "query");
+    if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
+    if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
+    if (!status && has_bias)
+      status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
+    if (status) return status;
+    P.dq = g.dq;
+    P.dk = g.dk;
+    P.dv = g.dv;
+    P.write_dq = g.dq.ptr != nullptr;
+    P.write_dk = g.dk.ptr != nullptr;
+    P.write_dv = g.dv.ptr != nullptr;
+    P.lse = lse;
+    P.delta = delta;
+    P.mask = p.mask;
+    P.m_sb = p.mask_sb;
+    P.m_sr = p.mask_sr;
+    P.m_sc = p.mask_sc;
+    P.batch = p.batch;
+    P.rows = p.rows;
+    P.cols = p.cols;
+    P.heads = p.heads;
+    P.bias_groups = p.bias_groups;
+    P.q_tiles = (int)ceil_div(p.cols, kTile);
+    P.k_tiles = P.q_tiles;
+    P.groups = fused_groups(p);
+    P.tiles_per_group = (int)ceil_div(P.q_tiles, P.groups);
+    P.scale = p.scale;
+    const uint64_t plane_bytes = align256(uint64_t(P.groups) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
+    if (P.groups > 1) {
+      P.dk_parts = reinterpret_cast<float*>(base + layout.pair_parts);
+      P.dv_parts = reinterpret_cast<float*>(base + layout.pair_parts + plane_bytes);
+    }
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.groups);
+    auto go = [&](auto kernel) -> int {
+      const int rc = reserve_smem(kernel, kFSmemBytes);
+      if (rc) return rc;
+      kernel<<<grid, kFThreads, kFSmemBytes, stream>>>(P);
+      count_launch();
+      return check_launch("tcgen05 dQ/dK/dV");
+    };
+    status = has_bias ? go(ta_bwd_fused_kernel<T, true>) : go(ta_bwd_fused_kernel<T, false>);
+    if (status) return status;
+    if (P.groups > 1) {
+      const int64_t vectors = int64_t(p.batch) * p.rows * p.cols * p.heads;
+      if (g.dk.ptr) {
+        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dk_parts, P.groups, g.dk, p.scale,
+                                                                                          p.batch, p.rows, p.cols, p.heads);
+        count_launch();
+        status = check_launch("tcgen05 dK reduce");
+        if (status) return status;
+      }
+      if (g.dv.ptr) {
+        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dv_parts, P.groups, g.dv, 1.f,
+                                                                                          p.batch, p.rows, p.cols, p.heads);
+        count_launch();
+        status = check_launch("tcgen05 dV reduce");
+        if (status) return status;
+      }
+    }
+  }
+
+  if (!fused && (g.dq.ptr || row_bias_grad)) {
     DqParams P{};
     status = encode_pair(&P.map_q, p, p.q, kTile, "query");
     if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
@@ -1272,7 +1764,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     if (status) return status;
   }
 
-  if (g.dk.ptr || g.dv.ptr) {
+  if (!fused && (g.dk.ptr || g.dv.ptr)) {
     DkvParams P{};
     status = encode_pair(&P.map_k, p, p.k, kTile, "key");
     if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
@@ -1358,10 +1850,6 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     status = check_launch("tcgen05 shared-bias reduce");
     if (status) return status;
   }
-  (void)map_q128;
-  (void)map_d128;
-  (void)map_k128;
-  (void)map_v128;
   return OOPS_TA_OK;
 }
 

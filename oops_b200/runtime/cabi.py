@@ -17,6 +17,7 @@ from torch import Tensor
 ABI_VERSION = 1
 F32, F16, BF16 = 0, 1, 2
 FLAG_FORCE_GENERIC = 1
+FLAG_SPLIT_REVERSE = 4
 FLAG_ALLOW_TF32 = 2
 
 STATUS_OK = 0
