@@ -798,7 +798,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
   } else if (warp < kElemWarps && (warp >> 3) < n_tiles) {
     const int w = warp >> 3;           // key tile
     const int half = (warp >> 2) & 1;  // which 32 of the step's 64 queries
-    const int wg = warp >> 2;
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tile_t = tmem_base + lane_field + w * kTileCols;
@@ -938,15 +937,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
 // ---------------------------------------------------------------------------------------------
 // fused dQ / dK / dV kernel: one pass over the score tiles of a pair row
 // ---------------------------------------------------------------------------------------------
-// CTA = (batch, row, head, group of up to 6 query tiles).  For every key tile and every query tile of the group:
+// CTA = (batch, row, head), rows of at most 6 query tiles (768 columns).  For every key tile and every query tile:
 // S = Q K^T and dP = dO V^T (128 x 128, tensor memory) -> the four warpgroups (a thread owns a query, a warpgroup
 // 32 of the 128 keys) compute P and dS once and write them, 16-bit, into two shared-memory images whose rows
 // are queries and whose 128-byte-swizzled columns are keys.  The tensor core reads those images three ways:
 // dV += P^T dO and dK += dS^T Q take them as MN-major A operands (M = keys), dQ += dS K as a K-major A operand
-// (M = queries).  dQ of all query tiles of the group, dK and dV of the current key tile stay in tensor memory:
+// (M = queries).  dQ of all query tiles, dK and dV of the current key tile stay in tensor memory:
 // S 128 | dP 128 | dK 32 | dV 32 | dQ 6 x 32 = 512 columns.  One `ex2` per logit and five products, where the
-// separate dQ and dK/dV kernels spend two and seven.  With more than one group per row (more than 768 columns)
-// every group leaves f32 partial planes of dK and dV that a last kernel adds in a fixed order.
+// separate dQ and dK/dV kernels spend two and seven.  The images cost shared-memory bandwidth (64 KB written and
+// 96 KB read per 128 x 128 step), which is what bounds this kernel; longer rows would need f32 partial planes of
+// dK and dV per group of 6 query tiles and measured slower than the separate kernels, so they keep those.
 
 constexpr int kFMaxQTiles = 6;
 constexpr int kFThreads = 608;  // 16 element-wise warps, TMA producer, score issuer, accumulation issuer
@@ -987,14 +987,12 @@ constexpr int kFSmemBytes = FSmem::total + 1024;
 struct FParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
   oops_ta_pair dq, dk, dv;
-  float* dk_parts;  // [groups][batch][rows][cols][heads][32] f32, used when groups > 1
-  float* dv_parts;
   const float* lse;
   const float* delta;
   const uint8_t* mask;
   int64_t m_sb, m_sr, m_sc;
   int batch, rows, cols, heads, bias_groups;
-  int q_tiles, k_tiles, groups, tiles_per_group;
+  int q_tiles, k_tiles;
   int write_dq, write_dk, write_dv;
   float scale;
 };
@@ -1012,14 +1010,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
-  const int group = idx % P.groups;
-  idx /= P.groups;
   const int h = idx % P.heads;
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
-  const int qt0 = group * P.tiles_per_group;
-  const int nq = min(P.tiles_per_group, P.q_tiles - qt0);
+  const int qt0 = 0;
+  const int nq = P.q_tiles;
   const int KT = P.k_tiles;
   const int steps = KT * nq;  // step s: key tile s / nq, query tile qt0 + s % nq
   const int g = P.bias_groups == 1 ? 0 : r;
@@ -1115,7 +1111,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
       bool ok = true;
+#ifdef TA_PROFILE_WAITS
+      long long f_wait = 0, f_issue = 0;
+      const long long f_start = clock64();
+#endif
       for (int s = 0; s < steps && ok; ++s) {
+        TB_CLOCK(f0);
         const int kt = s / nq, qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok && s % nq == 0) {
@@ -1125,6 +1126,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (ok && s > 0) ok = mbar_wait(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
+        TB_CLOCK(f1);
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);
         const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);
         const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);
@@ -1136,7 +1138,13 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           mma_ss(tmem_base + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
         mma_commit(bar(FSmem::sd_full));
+#ifdef TA_PROFILE_WAITS
+        f_wait += f1 - f0; f_issue += clock64() - f1;
+#endif
       }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(36, f_wait); TB_ADD(37, f_issue); TB_ADD(38, clock64() - f_start); TB_ADD(39, steps);
+#endif
     }
   } else if (warp == kFAccWarp) {
     if (lane == 0) {
@@ -1144,7 +1152,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       constexpr uint32_t idesc_t = instr_desc(fmt, 1, 1, kTile, kHeadDim);  // A = image^T (M = keys), B MN-major
       constexpr uint32_t idesc_q = instr_desc(fmt, 0, 1, kTile, kHeadDim);  // A = image (M = queries), B MN-major
       bool ok = true;
+#ifdef TA_PROFILE_WAITS
+      long long g_wait = 0, g_issue = 0;
+      const long long g_start = clock64();
+#endif
       for (int s = 0; s < steps && ok; ++s) {
+        TB_CLOCK(g0);
         const int kt = s / nq, qi = s % nq, qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
@@ -1153,6 +1166,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (ok && qi == 0 && kt > 0) ok = mbar_wait(bar(FSmem::dkv_free), (kt - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
+        TB_CLOCK(g1);
         const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss;
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);     // MN-major B
         const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);  // MN-major B
@@ -1172,7 +1186,13 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         mma_commit(bar(FSmem::pds_done));
         mma_commit(bar(FSmem::qd_empty + qs));
         if (qi == nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
+#ifdef TA_PROFILE_WAITS
+        g_wait += g1 - g0; g_issue += clock64() - g1;
+#endif
       }
+#ifdef TA_PROFILE_WAITS
+      TB_ADD(40, g_wait); TB_ADD(41, g_issue); TB_ADD(42, clock64() - g_start);
+#endif
     }
   } else if (warp < 16) {
     const int wg = warp >> 2;  // 32 of the step's 128 keys
@@ -1204,24 +1224,20 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       if (key >= P.cols) return;
       const bool wanted = wg == 0 ? P.write_dk != 0 : P.write_dv != 0;
       if (!wanted) return;
-      if (P.groups > 1) {
-        float* dst = (wg == 0 ? P.dk_parts : P.dv_parts) +
-                     ((((int64_t(group) * P.batch + b) * P.rows + r) * P.cols + key) * P.heads + h) * kHeadDim;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
-                                                           __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
-      } else {
-        const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
-        T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
-        store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
-      }
+      const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
+      T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
+      store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
     };
     float lse_next, delta_next;
     fetch_stats(0, lse_next, delta_next);
     bool ok = true;
+#ifdef TA_PROFILE_WAITS
+    uint32_t wc[4] = {0, 0, 0, 0};
+    const long long w_start = clock64();
+#endif
 
     for (int s = 0; s < steps && ok; ++s) {
+      TB_CLOCK(w0);
       const int kt = s / nq, qi = s % nq, slot = s & 1;
       const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
       fetch_stats(s + 1, lse_next, delta_next);
@@ -1244,6 +1260,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       if (ok && HAS_BIAS) ok = mbar_wait(bar(FSmem::bias_full + slot), (s >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      TB_CLOCK(w1);
       // bias row of this query: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
       const uint8_t* bias_row = smem_gen + FSmem::bias + slot * kFBias + (wg >> 1) * kBiasStep + t * 128 +
                                 (((t & 7) ^ ((wg & 1) * 4)) << 4);
@@ -1278,6 +1295,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(FSmem::bias_empty + slot));
+      TB_CLOCK(w2);
       if (s > 0) {
         // the products of the previous step must have finished reading the two images
         ok = mbar_wait(bar(FSmem::pds_done), (s - 1) & 1, abort_flag);
@@ -1286,6 +1304,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         // ... which also completes dK and dV of the previous key tile when this step opens a new one
         if (qi == 0) store_key_tile(kt - 1);
       }
+      TB_CLOCK(w3);
       // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
       uint8_t* p_row = smem_gen + FSmem::ps + (wg >> 1) * 16384 + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
       uint8_t* ds_row = p_row + kFImage;
@@ -1298,7 +1317,16 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(bar(FSmem::pds_full));
+#ifdef TA_PROFILE_WAITS
+      wc[0] += uint32_t(w1 - w0); wc[1] += uint32_t(w2 - w1); wc[2] += uint32_t(w3 - w2); wc[3] += uint32_t(clock64() - w3);
+#endif
     }
+#ifdef TA_PROFILE_WAITS
+    if (t == 0) {
+      TB_ADD(43, wc[0]); TB_ADD(44, wc[1]); TB_ADD(45, wc[2]); TB_ADD(46, wc[3]); TB_ADD(47, clock64() - w_start);
+      TB_ADD(35, steps);
+    }
+#endif
 
     if (ok) ok = mbar_wait(bar(FSmem::pds_done), (steps - 1) & 1, abort_flag);
     if (ok) {
@@ -1318,35 +1346,6 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     }
   }
   teardown(abort_flag, tmem_base, kFScoreWarp);
-}
-
-// Adds the f32 partial planes of dK or dV in a fixed order: one thread per (batch, row, column, head) vector of 32.
-template <typename T>
-__global__ void reduce_pair_parts_kernel(const float* parts, int groups, oops_ta_pair out, float scale, int batch, int rows,
-                                         int cols, int heads) {
-  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t vectors = int64_t(batch) * rows * cols * heads;
-  if (i >= vectors) return;
-  float total[32];
-#pragma unroll
-  for (int d = 0; d < 32; ++d) total[d] = 0.f;
-  for (int p = 0; p < groups; ++p) {
-    const float4* src = reinterpret_cast<const float4*>(parts + (int64_t(p) * vectors + i) * 32);
-#pragma unroll
-    for (int d = 0; d < 8; ++d) {
-      const float4 v = src[d];
-      total[4 * d] += v.x; total[4 * d + 1] += v.y; total[4 * d + 2] += v.z; total[4 * d + 3] += v.w;
-    }
-  }
-  const int h = i % heads;
-  const int c = (i / heads) % cols;
-  const int r = (i / (int64_t(heads) * cols)) % rows;
-  const int64_t b = i / (int64_t(heads) * cols * rows);
-  uint32_t acc[32];
-#pragma unroll
-  for (int d = 0; d < 32; ++d) acc[d] = __float_as_uint(total[d]);
-  T* dst = reinterpret_cast<T*>(out.ptr) + b * out.sb + int64_t(r) * out.sr + int64_t(c) * out.sc + h * out.sh;
-  store_row32<T>(dst, acc, scale, pair_vec_ok(out));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1589,17 +1588,17 @@ int bias_parts(const oops_ta_problem& p) {
   return (int)parts;
 }
 
-// The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient.
+// The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient, on rows
+// whose dQ accumulators fit in tensor memory (at most 6 query tiles).
 bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
   if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
   if (g.dbias && p.bias_groups > 1) return false;
+  if (ceil_div(p.cols, kTile) > kFMaxQTiles) return false;
   return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
 }
 
-int fused_groups(const oops_ta_problem& p) { return (int)ceil_div(ceil_div(p.cols, kTile), kFMaxQTiles); }
-
 struct Layout {
-  uint64_t delta, bias_t, parts, pair_parts, total;
+  uint64_t delta, bias_t, parts, total;
 };
 
 Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
@@ -1611,9 +1610,6 @@ Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
   const bool fused = fused_applies(p, g);
   if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr) && !fused)
     at += align256(uint64_t(p.batch) * p.bias_groups * p.heads * p.cols * padded_cols(p) * 2);
-  l.pair_parts = at;  // f32 partial planes of dK, then of dV, one per query group
-  if (fused && fused_groups(p) > 1)
-    at += 2 * align256(uint64_t(fused_groups(p)) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
   l.parts = at;
   if (g.dbias && p.bias_groups == 1)
     at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
@@ -1688,15 +1684,8 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.bias_groups = p.bias_groups;
     P.q_tiles = (int)ceil_div(p.cols, kTile);
     P.k_tiles = P.q_tiles;
-    P.groups = fused_groups(p);
-    P.tiles_per_group = (int)ceil_div(P.q_tiles, P.groups);
     P.scale = p.scale;
-    const uint64_t plane_bytes = align256(uint64_t(P.groups) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
-    if (P.groups > 1) {
-      P.dk_parts = reinterpret_cast<float*>(base + layout.pair_parts);
-      P.dv_parts = reinterpret_cast<float*>(base + layout.pair_parts + plane_bytes);
-    }
-    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.groups);
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads);
     auto go = [&](auto kernel) -> int {
       const int rc = reserve_smem(kernel, kFSmemBytes);
       if (rc) return rc;
@@ -1706,23 +1695,6 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     };
     status = has_bias ? go(ta_bwd_fused_kernel<T, true>) : go(ta_bwd_fused_kernel<T, false>);
     if (status) return status;
-    if (P.groups > 1) {
-      const int64_t vectors = int64_t(p.batch) * p.rows * p.cols * p.heads;
-      if (g.dk.ptr) {
-        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dk_parts, P.groups, g.dk, p.scale,
-                                                                                          p.batch, p.rows, p.cols, p.heads);
-        count_launch();
-        status = check_launch("tcgen05 dK reduce");
-        if (status) return status;
-      }
-      if (g.dv.ptr) {
-        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dv_parts, P.groups, g.dv, 1.f,
-                                                                                          p.batch, p.rows, p.cols, p.heads);
-        count_launch();
-        status = check_launch("tcgen05 dV reduce");
-        if (status) return status;
-      }
-    }
   }
 
   if (!fused && (g.dq.ptr || row_bias_grad)) {

@@ -15,7 +15,7 @@ import pytest
 import torch
 
 from oops_b200 import NestedTensor, triangle_attention
-from oops_b200.attention.triangle.triangle_attention import layout_agnostic_kernels
+from oops_b200.attention.triangle.triangle_attention import layout_agnostic_kernels, separate_reverse_kernels
 from oracle import triangle_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -607,6 +607,33 @@ def test_config4_ending_node_ragged(cuda):
     grads = torch.autograd.grad(values, [leaves[n] for n in ("q", "k", "v", "bias")], upstream.to(cuda))
     for name, grad in zip(("q", "k", "v", "bias"), grads):
         assert_within(grad, want[name], 2e-2 * max(1.0, float(want[name].abs().max())), f"d{name}")
+
+
+@pytest.mark.parametrize("n,valid,bias_kind", [(768, None, "shared"), (300, 260, "shared"), (200, 150, "none"), (136, None, "full")])
+def test_single_pass_reverse_matches_separate_kernels(cuda, n, valid, bias_kind):
+    """Rows of at most 768 columns take one kernel for dQ, dK and dV; the separate dQ and dK/dV kernels stay
+    reachable through a flag.  Both must give the same gradients (same products, same rounding points; only the
+    order of the f32 accumulation over tiles may differ)."""
+    q, k, v, bias, mask, upstream = baseline_inputs(n, torch.bfloat16, valid=valid, seed=21)
+    if valid is not None:
+        k[:, :, valid:] = float("inf")  # dropped keys may hold anything
+        v[:, :, valid:] = float("nan")
+    if bias_kind == "none":
+        bias = None
+    elif bias_kind == "full":
+        bias = torch.randn(1, n, 4, n, n, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    dev = [None if t is None else t.to(cuda) for t in (q, k, v, bias)]
+    results = []
+    for split in (False, True):
+        leaves = [t.detach().requires_grad_(True) for t in dev[:3]]
+        with separate_reverse_kernels(split):
+            out = triangle_attention(leaves[0], leaves[1], leaves[2], mask.to(cuda), dev[3])
+            results.append(torch.autograd.grad(out, leaves, upstream.to(cuda)))
+    live = slice(0, valid)
+    for name, single, separate in zip(("dq", "dk", "dv"), *results):
+        single, separate = single[:, live, live].float(), separate[:, live, live].float()
+        assert torch.isfinite(single).all(), name
+        assert_within(single, separate, 1e-2 * max(1.0, float(separate.abs().max())), name)
 
 
 def test_config5_full_size_properties(cuda):
