@@ -117,6 +117,25 @@ __device__ __forceinline__ uint32_t ldg_u8_here(const uint8_t* p) {
   return v;
 }
 
+// Four words from global memory when `take` is set, zeros otherwise; like the loads above it keeps its place and its
+// result is not touched before the caller uses it.
+__device__ __forceinline__ uint4 ldg_v4_here_if(const void* p, bool take) {
+  uint4 v;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.u32 p, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\t"
+      "mov.u32 %1, 0;\n\t"
+      "mov.u32 %2, 0;\n\t"
+      "mov.u32 %3, 0;\n\t"
+      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t"
+      "}\n"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p), "r"(uint32_t(take)));
+  return v;
+}
+
 // ---- proxies and fences ------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -188,6 +188,24 @@ __device__ __forceinline__ void score_grad8(const uint32_t* sraw, const uint32_t
   }
 }
 
+// Same with the eight bias values already in registers (four packed words).
+template <typename T, bool HAS_BIAS>
+__device__ __forceinline__ void score_grad8_words(const uint32_t* sraw, const uint32_t* draw, const uint4 bias_words, f32x2 c2,
+                                                  f32x2 log2e2, f32x2 nl, f32x2 nd, f32x2* p2, f32x2* ds2) {
+  const uint32_t bw[4] = {bias_words.x, bias_words.y, bias_words.z, bias_words.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const f32x2 s2 = pack2(__uint_as_float(sraw[2 * i]), __uint_as_float(sraw[2 * i + 1]));
+    const f32x2 d2 = pack2(__uint_as_float(draw[2 * i]), __uint_as_float(draw[2 * i + 1]));
+    const f32x2 offset = HAS_BIAS ? fma2(Half2<T>::widen(bw[i]), log2e2, nl) : nl;
+    float lo, hi;
+    unpack2(fma2(s2, c2, offset), lo, hi);
+    const f32x2 p = pack2(ex2(lo), ex2(hi));
+    p2[i] = p;
+    ds2[i] = mul2(p, add2(d2, nd));
+  }
+}
+
 __device__ __forceinline__ f32x2 select2(f32x2 v, uint32_t bits, int at) {
   float lo, hi;
   unpack2(v, lo, hi);
@@ -952,37 +970,40 @@ constexpr int kFMaxQTiles = 6;
 constexpr int kFThreads = 608;  // 16 element-wise warps, TMA producer, score issuer, accumulation issuer
 constexpr int kFProducerWarp = 16, kFScoreWarp = 17, kFAccWarp = 18;
 constexpr int kFImage = 2 * 16384;       // P or dS of a step: two 64-key halves of 128 rows x 128 bytes
-constexpr int kFBias = 2 * kBiasStep;    // 128 x 128 bias tile as two 64-key boxes
+constexpr int kFBias = 2 * kBiasStep;    // 128 x 128 bias tile as two 64-key boxes (staging: copied to registers at once)
+constexpr int kFKeepWords = 128;         // keep-bit table of a row
 
 struct FSmem {
   static constexpr int q = 0;                          // [3] 128 x 32 (a slot is held until the step's dK product ends)
   static constexpr int dout = q + 3 * kBigTile;        // [3]
   static constexpr int k = dout + 3 * kBigTile;        // [2]
   static constexpr int v = k + 2 * kBigTile;           // [2]
-  static constexpr int ps = v + 2 * kBigTile;          // P image
-  static constexpr int dss = ps + kFImage;             // dS image
-  static constexpr int bias = dss + kFImage;           // [2]
-  static constexpr int bars = bias + 2 * kFBias;
+  static constexpr int ps = v + 2 * kBigTile;          // P image (read by the dV products only, freed early)
+  static constexpr int dss = ps + kFImage;             // [2] dS image
+  static constexpr int bias = dss + 2 * kFImage;       // one staging tile
+  static constexpr int bars = bias + kFBias;
   static constexpr int qd_full = 0;                    // [3]
   static constexpr int qd_empty = qd_full + 3;         // [3]
   static constexpr int kv_full = qd_empty + 3;         // [2]
   static constexpr int kv_empty = kv_full + 2;         // [2]
   static constexpr int k_ready = kv_empty + 2;         // [2] dropped keys' rows cleared (only with a dropping mask)
-  static constexpr int bias_full = k_ready + 2;        // [2]
-  static constexpr int bias_empty = bias_full + 2;     // [2]
-  static constexpr int sd_full = bias_empty + 2;       // S and dP of a step are in tensor memory
+  static constexpr int bias_full = k_ready + 2;
+  static constexpr int bias_empty = bias_full + 1;     // every warp has copied its words of the tile to registers
+  static constexpr int sd_full = bias_empty + 1;       // S and dP of a step are in tensor memory
   static constexpr int sd_free = sd_full + 1;          // all warps have read them
-  static constexpr int pds_full = sd_free + 1;         // the P and dS images are written
-  static constexpr int pds_done = pds_full + 1;        // the three accumulating products have consumed them
-  static constexpr int dkv_free = pds_done + 1;        // dK and dV of a finished key tile have been read out
+  static constexpr int pds_full = sd_free + 1;         // [2] the P and dS images of a buffer are written
+  static constexpr int pds_done = pds_full + 2;        // [2] the dK and dQ products have consumed the dS image
+  static constexpr int p_done = pds_done + 2;          // the dV products have consumed the P image
+  static constexpr int dkv_free = p_done + 1;          // dK and dV of a finished key tile have been read out
   static constexpr int num_bars = dkv_free + 1;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
   static constexpr int drop_flags = abort_flag + 4;    // [16]
   static constexpr int keep = drop_flags + 64;
-  static constexpr int total = keep + kMaxKeepWords * 4;
+  static constexpr int total = keep + kFKeepWords * 4;
 };
 constexpr int kFSmemBytes = FSmem::total + 1024;
+static_assert(kFSmemBytes <= 232448, "fused reverse kernel: shared memory over the per-CTA limit");
 
 struct FParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
@@ -1031,16 +1052,19 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       mbar_init(bar(FSmem::qd_empty + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(FSmem::pds_full + i), 16);
+      mbar_init(bar(FSmem::pds_done + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(bar(FSmem::kv_full + i), 1);
       mbar_init(bar(FSmem::kv_empty + i), 1);
       mbar_init(bar(FSmem::k_ready + i), 4);
-      mbar_init(bar(FSmem::bias_full + i), 1);
-      mbar_init(bar(FSmem::bias_empty + i), 16);
     }
+    mbar_init(bar(FSmem::p_done), 1);
+    mbar_init(bar(FSmem::bias_full), 1);
+    mbar_init(bar(FSmem::bias_empty), 16);
     mbar_init(bar(FSmem::sd_full), 1);
     mbar_init(bar(FSmem::sd_free), 16);
-    mbar_init(bar(FSmem::pds_full), 16);
-    mbar_init(bar(FSmem::pds_done), 1);
     mbar_init(bar(FSmem::dkv_free), 8);
     fence_barrier_init();
   }
@@ -1082,9 +1106,10 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   if (warp == kFProducerWarp) {
     if (lane == 0) {
       bool ok = true;
-      for (int s = 0; s < steps && ok; ++s) {
-        const int kt = s / nq, qt = qt0 + s % nq, slot = s & 1, qs = s % 3;
-        if (s % nq == 0) {
+      int kt = 0, qi = 0;
+      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
+        const int qt = qt0 + qi, qs = s % 3;
+        if (qi == 0) {
           const int ks = kt & 1;
           if (kt >= 2) ok = mbar_wait(bar(FSmem::kv_empty + ks), ((kt >> 1) - 1) & 1, abort_flag);
           if (!ok) break;
@@ -1098,12 +1123,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         tma_load_5d(smem_base + FSmem::q + qs * kBigTile, &P.map_q, bar(FSmem::qd_full + qs), 0, h, qt * kTile, r, b);
         tma_load_5d(smem_base + FSmem::dout + qs * kBigTile, &P.map_dout, bar(FSmem::qd_full + qs), 0, h, qt * kTile, r, b);
         if (HAS_BIAS) {
-          if (s >= 2) ok = mbar_wait(bar(FSmem::bias_empty + slot), ((s >> 1) - 1) & 1, abort_flag);
+          if (s >= 1) ok = mbar_wait(bar(FSmem::bias_empty), (s - 1) & 1, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(bar(FSmem::bias_full + slot), kFBias);
+          mbar_expect_tx(bar(FSmem::bias_full), kFBias);
           for (int box = 0; box < 2; ++box)
-            tma_load_5d(smem_base + FSmem::bias + slot * kFBias + box * kBiasStep, &P.map_bias, bar(FSmem::bias_full + slot),
-                        kt * kTile + box * 64, qt * kTile, h, g, b);
+            tma_load_5d(smem_base + FSmem::bias + box * kBiasStep, &P.map_bias, bar(FSmem::bias_full), kt * kTile + box * 64,
+                        qt * kTile, h, g, b);
         }
       }
     }
@@ -1115,11 +1140,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       long long f_wait = 0, f_issue = 0;
       const long long f_start = clock64();
 #endif
-      for (int s = 0; s < steps && ok; ++s) {
+      int kt = 0, qi = 0;
+      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
         TB_CLOCK(f0);
-        const int kt = s / nq, qs = s % 3, ks = kt & 1;
+        const int qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
-        if (ok && s % nq == 0) {
+        if (ok && qi == 0) {
           ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
           if (ok && signoff) ok = mbar_wait(bar(FSmem::k_ready + ks), (kt >> 1) & 1, abort_flag);
         }
@@ -1156,18 +1182,19 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       long long g_wait = 0, g_issue = 0;
       const long long g_start = clock64();
 #endif
-      for (int s = 0; s < steps && ok; ++s) {
+      int kt = 0, qi = 0;
+      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
         TB_CLOCK(g0);
-        const int kt = s / nq, qi = s % nq, qs = s % 3, ks = kt & 1;
+        const int qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
-        if (ok) ok = mbar_wait(bar(FSmem::pds_full), s & 1, abort_flag);
+        if (ok) ok = mbar_wait(bar(FSmem::pds_full + (s & 1)), (s >> 1) & 1, abort_flag);
         // dK and dV of the previous key tile must have been read out before they are overwritten
         if (ok && qi == 0 && kt > 0) ok = mbar_wait(bar(FSmem::dkv_free), (kt - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         TB_CLOCK(g1);
-        const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss;
+        const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss + (s & 1) * kFImage;
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);     // MN-major B
         const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);  // MN-major B
         const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);       // MN-major B
@@ -1175,6 +1202,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         for (int kk = 0; kk < kTile / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 128 q] dO[128 q x 32]
           mma_ss(tmem_base + kDvCol, smem_desc(ps + kk * 2048, 16384, 1024, kSwizzle128B), ddesc + uint64_t(kk * (1024 >> 4)),
                  idesc_t, (qi > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(bar(FSmem::p_done));
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 128 q] Q[128 q x 32]
           mma_ss(tmem_base + kDkCol, smem_desc(dss + kk * 2048, 16384, 1024, kSwizzle128B), qdesc + uint64_t(kk * (1024 >> 4)),
@@ -1183,7 +1211,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         for (int kk = 0; kk < kTile / 16; ++kk)  // dQ[128 q x 32] += dS[128 q x 128 k] K[128 k x 32]
           mma_ss(tmem_base + kDqCol + qi * kHeadDim, smem_desc(dss + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, kSwizzle128B),
                  kdesc + uint64_t(kk * (1024 >> 4)), idesc_q, (kt > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(bar(FSmem::pds_done));
+        mma_commit(bar(FSmem::pds_done + (s & 1)));
         mma_commit(bar(FSmem::qd_empty + qs));
         if (qi == nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
 #ifdef TA_PROFILE_WAITS
@@ -1203,10 +1231,10 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
     const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
     // statistics of this thread's query in the step's query tile, fetched one step ahead and left untouched till then
-    auto fetch_stats = [&](int s, float& lse_raw, float& delta_raw) {
+    auto fetch_stats = [&](int s, int qi_of_s, float& lse_raw, float& delta_raw) {
       lse_raw = INFINITY;
       delta_raw = 0.f;
-      const int q = (qt0 + s % nq) * kTile + t;
+      const int q = (qt0 + qi_of_s) * kTile + t;
       if (s < steps && q < P.cols) {
         lse_raw = ldg_f32_here(P.lse + stat_base + q);
         delta_raw = ldg_f32_here(P.delta + stat_base + q);
@@ -1229,21 +1257,42 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
     };
     float lse_next, delta_next;
-    fetch_stats(0, lse_next, delta_next);
+    fetch_stats(0, 0, lse_next, delta_next);
     bool ok = true;
 #ifdef TA_PROFILE_WAITS
-    uint32_t wc[4] = {0, 0, 0, 0};
+    uint32_t wc[4] = {0, 0, 0, 0}, wx[3] = {0, 0, 0}, wy[2] = {0, 0};
     const long long w_start = clock64();
 #endif
 
-    for (int s = 0; s < steps && ok; ++s) {
+    // bias row of this thread's query in the staging tile: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
+    const uint8_t* bias_row = smem_gen + FSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
+
+    int kt = 0, qi = 0;
+    for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
       TB_CLOCK(w0);
-      const int kt = s / nq, qi = s % nq, slot = s & 1;
+      const int buf = s & 1;
       const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
-      fetch_stats(s + 1, lse_next, delta_next);
+      fetch_stats(s + 1, qi + 1 == nq ? 0 : qi + 1, lse_next, delta_next);
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
-      const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
       const uint32_t bits = has_bits ? keep_words[kt * 4 + wg] : 0xffffffffu;
+      // The step's bias words go to registers at once and the staging tile is handed back, so that the next
+      // tile's copy runs under this step's arithmetic.
+      uint4 bias_words[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      TB_CLOCK(wA);
+      if (HAS_BIAS) {
+        ok = mbar_wait(bar(FSmem::bias_full), s & 1, abort_flag);
+        if (!ok) break;
+#ifdef TA_PROFILE_WAITS
+        wy[0] += uint32_t(wA - w0); wy[1] += uint32_t(clock64() - wA);
+#endif
+#pragma unroll
+        for (int c = 0; c < 4; ++c) bias_words[c] = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, c));
+        // the loads must have returned before the tile is handed back (the copy of the next tile may land at once)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          asm volatile("" ::"r"(bias_words[c].x), "r"(bias_words[c].y), "r"(bias_words[c].z), "r"(bias_words[c].w) : "memory");
+        mbar_arrive_warp(bar(FSmem::bias_empty));
+      }
       if (signoff && qi == 0 && warp < 4) {
         // key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory
         const int ks = kt & 1;
@@ -1256,15 +1305,22 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         fence_proxy_async_smem();
         mbar_arrive_warp(bar(FSmem::k_ready + ks));
       }
-      ok = mbar_wait(bar(FSmem::sd_full), s & 1, abort_flag);
-      if (ok && HAS_BIAS) ok = mbar_wait(bar(FSmem::bias_full + slot), (s >> 1) & 1, abort_flag);
+      TB_CLOCK(w0a);
+      // this step's dS image was last read by the products of step s - 2, the P image by the dV products of s - 1
+      if (s >= 2) ok = mbar_wait(bar(FSmem::pds_done + buf), ((s >> 1) - 1) & 1, abort_flag);
+      TB_CLOCK(w0b);
+      if (ok) ok = mbar_wait(bar(FSmem::sd_full), s & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       TB_CLOCK(w1);
-      // bias row of this query: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
-      const uint8_t* bias_row = smem_gen + FSmem::bias + slot * kFBias + (wg >> 1) * kBiasStep + t * 128 +
-                                (((t & 7) ^ ((wg & 1) * 4)) << 4);
-      uint32_t p_packed[16], ds_packed[16];
+#ifdef TA_PROFILE_WAITS
+      wx[0] += uint32_t(w0a - w0); wx[1] += uint32_t(w0b - w0a); wx[2] += uint32_t(w1 - w0b);
+#endif
+      // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
+      const int row_at = (wg >> 1) * 16384 + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
+      uint8_t* p_row = smem_gen + FSmem::ps + row_at;
+      uint8_t* ds_row = smem_gen + FSmem::dss + buf * kFImage + row_at;
+      uint32_t p_packed[16];
 #pragma unroll
       for (int round = 0; round < 2; ++round) {
         uint32_t sraw[16], draw[16];
@@ -1279,7 +1335,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         for (int i8 = 0; i8 < 2; ++i8) {
           const int c8 = round * 2 + i8;
           f32x2 p2[4], ds2[4];
-          score_grad8<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, swizzled_chunk(bias_row, c8), c2, log2e2, nl2, nd2, p2, ds2);
+          score_grad8_words<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_words[c8], c2, log2e2, nl1, nd1, p2, ds2);
           if (bits != 0xffffffffu) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -1288,35 +1344,31 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
             }
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
-            ds_packed[c8 * 4 + i] = pack16<T>(ds2[i]);
-          }
+          for (int i = 0; i < 4; ++i) p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
+          *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(ds_row, c8))) =
+              make_uint4(pack16<T>(ds2[0]), pack16<T>(ds2[1]), pack16<T>(ds2[2]), pack16<T>(ds2[3]));
         }
       }
-      if (HAS_BIAS) mbar_arrive_warp(bar(FSmem::bias_empty + slot));
-      TB_CLOCK(w2);
-      if (s > 0) {
-        // the products of the previous step must have finished reading the two images
-        ok = mbar_wait(bar(FSmem::pds_done), (s - 1) & 1, abort_flag);
+      // the single P image is free once the dV products of the previous step have read it; by now they have
+      if (s >= 1) {
+        ok = mbar_wait(bar(FSmem::p_done), (s - 1) & 1, abort_flag);
         if (!ok) break;
-        tc_fence_after_sync();
-        // ... which also completes dK and dV of the previous key tile when this step opens a new one
-        if (qi == 0) store_key_tile(kt - 1);
       }
-      TB_CLOCK(w3);
-      // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
-      uint8_t* p_row = smem_gen + FSmem::ps + (wg >> 1) * 16384 + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
-      uint8_t* ds_row = p_row + kFImage;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
             make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
-        *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(ds_row, c))) =
-            make_uint4(ds_packed[4 * c], ds_packed[4 * c + 1], ds_packed[4 * c + 2], ds_packed[4 * c + 3]);
+      TB_CLOCK(w2);
+      if (qi == 0 && s > 0) {
+        // a new key tile: dK and dV of the previous one are complete once the products of step s - 1 are
+        ok = mbar_wait(bar(FSmem::pds_done + ((s - 1) & 1)), ((s - 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        store_key_tile(kt - 1);
       }
+      TB_CLOCK(w3);
       fence_proxy_async_smem();
-      mbar_arrive_warp(bar(FSmem::pds_full));
+      mbar_arrive_warp(bar(FSmem::pds_full + buf));
 #ifdef TA_PROFILE_WAITS
       wc[0] += uint32_t(w1 - w0); wc[1] += uint32_t(w2 - w1); wc[2] += uint32_t(w3 - w2); wc[3] += uint32_t(clock64() - w3);
 #endif
@@ -1324,11 +1376,14 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
 #ifdef TA_PROFILE_WAITS
     if (t == 0) {
       TB_ADD(43, wc[0]); TB_ADD(44, wc[1]); TB_ADD(45, wc[2]); TB_ADD(46, wc[3]); TB_ADD(47, clock64() - w_start);
+      TB_ADD(32, wx[0]); TB_ADD(33, wx[1]); TB_ADD(34, wx[2]); TB_ADD(30, wy[0]); TB_ADD(31, wy[1]);
       TB_ADD(35, steps);
     }
 #endif
 
-    if (ok) ok = mbar_wait(bar(FSmem::pds_done), (steps - 1) & 1, abort_flag);
+    // every product has finished when the products of the last two steps have
+    if (ok && steps > 1) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 2) & 1)), ((steps - 2) >> 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 1) & 1)), ((steps - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       store_key_tile(KT - 1);
