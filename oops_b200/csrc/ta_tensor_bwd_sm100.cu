@@ -955,16 +955,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
 // ---------------------------------------------------------------------------------------------
 // fused dQ / dK / dV kernel: one pass over the score tiles of a pair row
 // ---------------------------------------------------------------------------------------------
-// CTA = (batch, row, head), rows of at most 6 query tiles (768 columns).  For every key tile and every query tile:
+// CTA = (batch, row, head, group of up to 6 query tiles).  For every key tile and every query tile of the group:
 // S = Q K^T and dP = dO V^T (128 x 128, tensor memory) -> the four warpgroups (a thread owns a query, a warpgroup
 // 32 of the 128 keys) compute P and dS once and write them, 16-bit, into two shared-memory images whose rows
 // are queries and whose 128-byte-swizzled columns are keys.  The tensor core reads those images three ways:
 // dV += P^T dO and dK += dS^T Q take them as MN-major A operands (M = keys), dQ += dS K as a K-major A operand
-// (M = queries).  dQ of all query tiles, dK and dV of the current key tile stay in tensor memory:
+// (M = queries).  dQ of the group's query tiles, dK and dV of the current key tile stay in tensor memory:
 // S 128 | dP 128 | dK 32 | dV 32 | dQ 6 x 32 = 512 columns.  One `ex2` per logit and five products, where the
 // separate dQ and dK/dV kernels spend two and seven.  The images cost shared-memory bandwidth (64 KB written and
-// 96 KB read per 128 x 128 step), which is what bounds this kernel; longer rows would need f32 partial planes of
-// dK and dV per group of 6 query tiles and measured slower than the separate kernels, so they keep those.
+// 96 KB read per 128 x 128 step), which is what bounds this kernel.  Rows of more than 768 columns are split into
+// groups; every group leaves f32 partial planes of dK and dV that a last kernel adds in a fixed order.
 
 constexpr int kFMaxQTiles = 6;
 constexpr int kFThreads = 608;  // 16 element-wise warps, TMA producer, score issuer, accumulation issuer
@@ -1008,12 +1008,14 @@ static_assert(kFSmemBytes <= 232448, "fused reverse kernel: shared memory over t
 struct FParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
   oops_ta_pair dq, dk, dv;
+  float* dk_parts;  // [groups][batch][rows][cols][heads][32] f32, used when groups > 1
+  float* dv_parts;
   const float* lse;
   const float* delta;
   const uint8_t* mask;
   int64_t m_sb, m_sr, m_sc;
   int batch, rows, cols, heads, bias_groups;
-  int q_tiles, k_tiles;
+  int q_tiles, k_tiles, groups, tiles_per_group;
   int write_dq, write_dk, write_dv;
   float scale;
 };
@@ -1031,12 +1033,14 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
+  const int group = idx % P.groups;
+  idx /= P.groups;
   const int h = idx % P.heads;
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
-  const int qt0 = 0;
-  const int nq = P.q_tiles;
+  const int qt0 = group * P.tiles_per_group;
+  const int nq = min(P.tiles_per_group, P.q_tiles - qt0);
   const int KT = P.k_tiles;
   const int steps = KT * nq;  // step s: key tile s / nq, query tile qt0 + s % nq
   const int g = P.bias_groups == 1 ? 0 : r;
@@ -1252,9 +1256,18 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       if (key >= P.cols) return;
       const bool wanted = wg == 0 ? P.write_dk != 0 : P.write_dv != 0;
       if (!wanted) return;
-      const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
-      T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
-      store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
+      if (P.groups > 1) {
+        float* dst = (wg == 0 ? P.dk_parts : P.dv_parts) +
+                     ((((int64_t(group) * P.batch + b) * P.rows + r) * P.cols + key) * P.heads + h) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                                           __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+      } else {
+        const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
+        T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
+        store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
+      }
     };
     float lse_next, delta_next;
     fetch_stats(0, 0, lse_next, delta_next);
@@ -1401,6 +1414,35 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     }
   }
   teardown(abort_flag, tmem_base, kFScoreWarp);
+}
+
+// Adds the f32 partial planes of dK or dV in a fixed order: one thread per (batch, row, column, head) vector of 32.
+template <typename T>
+__global__ void reduce_pair_parts_kernel(const float* parts, int groups, oops_ta_pair out, float scale, int batch, int rows,
+                                         int cols, int heads) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t vectors = int64_t(batch) * rows * cols * heads;
+  if (i >= vectors) return;
+  float total[32];
+#pragma unroll
+  for (int d = 0; d < 32; ++d) total[d] = 0.f;
+  for (int p = 0; p < groups; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(parts + (int64_t(p) * vectors + i) * 32);
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      const float4 v = src[d];
+      total[4 * d] += v.x; total[4 * d + 1] += v.y; total[4 * d + 2] += v.z; total[4 * d + 3] += v.w;
+    }
+  }
+  const int h = i % heads;
+  const int c = (i / heads) % cols;
+  const int r = (i / (int64_t(heads) * cols)) % rows;
+  const int64_t b = i / (int64_t(heads) * cols * rows);
+  uint32_t acc[32];
+#pragma unroll
+  for (int d = 0; d < 32; ++d) acc[d] = __float_as_uint(total[d]);
+  T* dst = reinterpret_cast<T*>(out.ptr) + b * out.sb + int64_t(r) * out.sr + int64_t(c) * out.sc + h * out.sh;
+  store_row32<T>(dst, acc, scale, pair_vec_ok(out));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1644,16 +1686,23 @@ int bias_parts(const oops_ta_problem& p) {
 }
 
 // The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient, on rows
-// whose dQ accumulators fit in tensor memory (at most 6 query tiles).
+// whose keep-bit table fits its shared memory (4096 columns).
 bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
   if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
   if (g.dbias && p.bias_groups > 1) return false;
-  if (ceil_div(p.cols, kTile) > kFMaxQTiles) return false;
+  if (ceil_div(p.cols, 32) > kFKeepWords) return false;
   return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
 }
 
+// rows of more than 6 query tiles are split into groups of query tiles, one CTA each
+int fused_groups(const oops_ta_problem& p) { return (int)ceil_div(ceil_div(p.cols, kTile), kFMaxQTiles); }
+
+uint64_t fused_plane_bytes(const oops_ta_problem& p) {
+  return align256(uint64_t(fused_groups(p)) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
+}
+
 struct Layout {
-  uint64_t delta, bias_t, parts, total;
+  uint64_t delta, bias_t, pair_parts, parts, total;
 };
 
 Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
@@ -1665,6 +1714,8 @@ Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
   const bool fused = fused_applies(p, g);
   if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr) && !fused)
     at += align256(uint64_t(p.batch) * p.bias_groups * p.heads * p.cols * padded_cols(p) * 2);
+  l.pair_parts = at;  // f32 partial planes of dK, then of dV, one per group of query tiles
+  if (fused && fused_groups(p) > 1) at += 2 * fused_plane_bytes(p);
   l.parts = at;
   if (g.dbias && p.bias_groups == 1)
     at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
@@ -1739,8 +1790,14 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.bias_groups = p.bias_groups;
     P.q_tiles = (int)ceil_div(p.cols, kTile);
     P.k_tiles = P.q_tiles;
+    P.groups = fused_groups(p);
+    P.tiles_per_group = (int)ceil_div(P.q_tiles, P.groups);
     P.scale = p.scale;
-    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads);
+    if (P.groups > 1) {
+      P.dk_parts = reinterpret_cast<float*>(base + layout.pair_parts);
+      P.dv_parts = reinterpret_cast<float*>(base + layout.pair_parts + fused_plane_bytes(p));
+    }
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.groups);
     auto go = [&](auto kernel) -> int {
       const int rc = reserve_smem(kernel, kFSmemBytes);
       if (rc) return rc;
@@ -1750,6 +1807,23 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     };
     status = has_bias ? go(ta_bwd_fused_kernel<T, true>) : go(ta_bwd_fused_kernel<T, false>);
     if (status) return status;
+    if (P.groups > 1) {
+      const int64_t vectors = int64_t(p.batch) * p.rows * p.cols * p.heads;
+      if (g.dk.ptr) {
+        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dk_parts, P.groups, g.dk, p.scale,
+                                                                                          p.batch, p.rows, p.cols, p.heads);
+        count_launch();
+        status = check_launch("tcgen05 dK reduce");
+        if (status) return status;
+      }
+      if (g.dv.ptr) {
+        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dv_parts, P.groups, g.dv, 1.f,
+                                                                                          p.batch, p.rows, p.cols, p.heads);
+        count_launch();
+        status = check_launch("tcgen05 dV reduce");
+        if (status) return status;
+      }
+    }
   }
 
   if (!fused && (g.dq.ptr || row_bias_grad)) {
