@@ -282,13 +282,13 @@ def main():
         fwd_launches = (cabi.launch_count() - before) // args.steps
     fwd_flops_rank = flops(hi - lo, n, heads, dim, False)
     fwd_tflops = fwd_flops_rank / (ms_fwd * 1e-3) / 1e12
-    # ---- the three reverse-pass tensor kernels, each reached by asking for its gradients only ----
-    # (a call with one group of gradients launches the row-dot kernel, the bias transpose and that one tensor
-    # kernel; the two helpers are ~5 % of the group, so a group's rate slightly understates its tensor kernel)
+    # ---- the reverse-pass tensor kernels, each reached by asking for its gradients only ------------
+    # dQ, dK and dV together take the single-pass kernel (five products); the bias gradient its own (two).  A call
+    # also launches the row-dot kernel (and, for rows split into groups, the two partial-plane adds), a few percent
+    # of the group, so a group's rate slightly understates its tensor kernel.
     unit = flops(hi - lo, n, heads, dim, False) / 2.0  # one C x C x D product over this rank's rows
     groups = {}
-    for name, wanted, products in (("dq", "q", 3), ("dkv", "kv", 4), ("dbias", "b", 2)):
-        # only the leaves of this group require gradients, so the reverse call launches this group's kernel alone
+    for name, wanted, products in (("dqkv", "qkv", 5), ("dbias", "b", 2)):
         ql, kl, vl, bl = (t.detach().requires_grad_(c in wanted) for t, c in ((q, "q"), (k, "k"), (v, "v"), (bias_full, "b")))
         out_l = triangle_attention(ql, kl, vl, mask, bl)
         targets = [t for t in (ql, kl, vl, bl) if t.requires_grad]
@@ -314,16 +314,16 @@ def main():
         per_row = profile.get("%s_dram_bytes_per_row_n%d" % (kernel, n))
         return None if per_row is None else per_row * (hi - lo)
 
-    # the kernel with the largest share of a training step (ncu launch list): dK/dV
+    # the kernel with the largest share of a training step (ncu launch list): the single-pass dQ/dK/dV kernel
     roofline = {
-        "bound": "tensor", "kernel": "ta_bwd_dkv_kernel (timed as the dK/dV-only reverse call: %d launches, the two "
-        "helper kernels ~5 %% of it)" % groups["dkv"]["launches"],
-        "achieved": groups["dkv"]["tflops_per_gpu"], "peak": peak, "unit": "TFLOP/s",
-        "frac": groups["dkv"]["frac_of_bf16_peak"], "peak_kind": peak_kind, "ms": groups["dkv"]["ms"],
-        "traffic": traffic("dkv"),
+        "bound": "tensor", "kernel": "ta_bwd_fused_kernel (timed as the dQ+dK+dV reverse call: %d launches, the helper "
+        "kernels a few percent of it)" % groups["dqkv"]["launches"],
+        "achieved": groups["dqkv"]["tflops_per_gpu"], "peak": peak, "unit": "TFLOP/s",
+        "frac": groups["dqkv"]["frac_of_bf16_peak"], "peak_kind": peak_kind, "ms": groups["dqkv"]["ms"],
+        "traffic": traffic("dqkv"),
         "forward": {"kernel": "ta_fwd_kernel (one call; %d launch(es))" % fwd_launches, "achieved": fwd_tflops,
                     "frac": fwd_tflops / peak, "ms": ms_fwd, "traffic": traffic("forward")},
-        "dq": groups["dq"], "dbias": groups["dbias"],
+        "dbias": dict(groups["dbias"], traffic=traffic("dbias")),
     }
 
     line = {
