@@ -1685,20 +1685,21 @@ int bias_parts(const oops_ta_problem& p) {
   return (int)parts;
 }
 
-// The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient, on rows
-// whose keep-bit table fits its shared memory (4096 columns).
-bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
-  if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
-  if (g.dbias && p.bias_groups > 1) return false;
-  if (ceil_div(p.cols, 32) > kFKeepWords) return false;
-  return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
-}
-
 // rows of more than 6 query tiles are split into groups of query tiles, one CTA each
 int fused_groups(const oops_ta_problem& p) { return (int)ceil_div(ceil_div(p.cols, kTile), kFMaxQTiles); }
 
 uint64_t fused_plane_bytes(const oops_ta_problem& p) {
   return align256(uint64_t(fused_groups(p)) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
+}
+
+// The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient, on rows
+// whose keep-bit table fits its shared memory (4096 columns) and whose partial planes stay within 16 GiB of scratch.
+bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
+  if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
+  if (g.dbias && p.bias_groups > 1) return false;
+  if (ceil_div(p.cols, 32) > kFKeepWords) return false;
+  if (fused_groups(p) > 1 && 2 * fused_plane_bytes(p) > (uint64_t(16) << 30)) return false;
+  return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
 }
 
 struct Layout {
