@@ -113,7 +113,9 @@ def nested_case(reference, flatten):
 
 
 def main():
-    reference_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference>")
+    reference_root = Path(sys.argv[1])
     reference, flatten = load_reference_functions(reference_root)
     dense_case(reference, "dense_f32_shared_masked", seed=1, prefix=(2,), rows=4, cols=33, heads=2, dim=24,
                dtype=torch.float32, bias_kind="shared", mask_kind="random", compute_dtype=torch.float32)
