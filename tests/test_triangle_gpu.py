@@ -609,11 +609,16 @@ def test_config4_ending_node_ragged(cuda):
         assert_within(grad, want[name], 2e-2 * max(1.0, float(want[name].abs().max())), f"d{name}")
 
 
-@pytest.mark.parametrize("n,valid,bias_kind", [(768, None, "shared"), (300, 260, "shared"), (200, 150, "none"), (136, None, "full")])
+@pytest.mark.parametrize(
+    "n,valid,bias_kind",
+    [(768, None, "shared"), (300, 260, "shared"), (200, 150, "none"), (136, None, "full"),
+     (1000, 900, "shared"),   # 8 query tiles: two groups of 4, ragged last tile, f32 partial planes of dK and dV
+     (1664, None, "none")],   # 13 query tiles: groups of 5, 5 and 3
+)
 def test_single_pass_reverse_matches_separate_kernels(cuda, n, valid, bias_kind):
-    """Rows of at most 768 columns take one kernel for dQ, dK and dV; the separate dQ and dK/dV kernels stay
-    reachable through a flag.  Both must give the same gradients (same products, same rounding points; only the
-    order of the f32 accumulation over tiles may differ)."""
+    """Calls that want dQ, dK and dV take one kernel for all three (rows of more than 768 columns in groups of
+    query tiles); the separate dQ and dK/dV kernels stay reachable through a flag.  Both must give the same
+    gradients (same products, same rounding points; only the order of the f32 accumulation over tiles differs)."""
     q, k, v, bias, mask, upstream = baseline_inputs(n, torch.bfloat16, valid=valid, seed=21)
     if valid is not None:
         k[:, :, valid:] = float("inf")  # dropped keys may hold anything
