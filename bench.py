@@ -118,26 +118,42 @@ def make_inputs(n, heads, dim, row_lo, row_hi, seed):
     return q, k, v, upstream, bias_shard, mask
 
 
-def cpu_oracle_rate(n, heads, dim, budget_s, threads):
-    """Time the oracle's forward+backward on a bounded sample of rows; returns (TFLOP/s, rows, seconds)."""
-    from oracle import triangle_oracle as oracle
+class CpuOracle:
+    """The oracle's forward+backward on a bounded sample of pair rows (rows are independent), timed on the host."""
 
-    torch.set_num_threads(threads)
-    gen = torch.Generator().manual_seed(1)
-    bias = torch.randn(1, 1, heads, n, n, generator=gen)
+    def __init__(self, n, heads, dim, budget_s, threads):
+        from oracle import triangle_oracle as oracle
 
-    def run(rows):
-        q, k, v, up = (torch.randn(1, rows, n, heads, dim, generator=gen) * 0.5 for _ in range(4))
-        mask = torch.ones(1, rows, n, dtype=torch.bool)
+        self.oracle, self.n, self.heads, self.dim = oracle, n, heads, dim
+        torch.set_num_threads(threads)
+        self.gen = torch.Generator().manual_seed(1)
+        self.bias = torch.randn(1, 1, heads, n, n, generator=self.gen)
+        self._make(2)
+        self.run()  # warm-up
+        self._make(min(n, 16))
+        per_row = self.run() / self.rows  # rate at a size that no longer fits the caches
+        self._make(int(max(2, min(n, budget_s / max(per_row, 1e-6)))))
+
+    def _make(self, rows):
+        n, heads, dim = self.n, self.heads, self.dim
+        self.rows = rows
+        self.inputs = [torch.randn(1, rows, n, heads, dim, generator=self.gen) * 0.5 for _ in range(4)]
+        self.mask = torch.ones(1, rows, n, dtype=torch.bool)
+
+    def run(self):
+        q, k, v, up = self.inputs
         t0 = time.perf_counter()
-        oracle.forward_backward(q, k, v, mask, bias, up, budget_bytes=1 << 30)
+        self.oracle.forward_backward(q, k, v, self.mask, self.bias, up, budget_bytes=1 << 30)
         return time.perf_counter() - t0
 
-    run(1)  # warm-up
-    probe = run(2)
-    rows = int(max(2, min(n, budget_s / max(probe / 2, 1e-6))))
-    seconds = run(rows)
-    return flops(rows, n, heads, dim, True) / seconds / 1e12, rows, seconds
+    def rate(self):
+        seconds = self.run()
+        return flops(self.rows, self.n, self.heads, self.dim, True) / seconds / 1e12, self.rows, seconds
+
+
+def cpu_oracle_rate(n, heads, dim, budget_s, threads):
+    """One timed pass; returns (TFLOP/s, rows, seconds)."""
+    return CpuOracle(n, heads, dim, budget_s, threads).rate()
 
 
 def reference_arm(args, work):
@@ -147,12 +163,14 @@ def reference_arm(args, work):
         return
     n, heads, dim = work["n"], work["heads"], work["dim"]
     threads = os.cpu_count() or 1
+    # a step is a bounded sample of rows sized so that the whole run stays near two minutes
     budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    cpu = CpuOracle(n, heads, dim, budget, threads)
     for _ in range(args.warmup):
-        cpu_oracle_rate(n, heads, dim, budget / 4, threads)
+        cpu.run()
     rates, rows_used, secs = [], 0, []
     for _ in range(args.steps):
-        rate, rows_used, seconds = cpu_oracle_rate(n, heads, dim, budget, threads)
+        rate, rows_used, seconds = cpu.rate()
         rates.append(rate)
         secs.append(seconds)
     value = statistics.mean(rates)
