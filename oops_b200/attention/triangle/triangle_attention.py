@@ -62,22 +62,29 @@ def triangle_attention(
         OOpsUnsupportedError: unsupported device, dtype, layout, empty size,
             launch limit, or forward-mode differentiation.
     """
-    if is_nested(query):
-        if not is_nested(key) or not is_nested(value):
-            raise ValueError("triangle_attention query, key, and value must all use the same NestedTensor layout")
-        if mask is not None and not is_nested(mask):
-            raise ValueError("triangle_attention mask must use the same NestedTensor layout as nested query/key/value")
-        if triangle_bias is not None and not is_nested(triangle_bias):
-            raise ValueError(
-                "triangle_attention triangle_bias must use a compatible NestedTensor layout with nested query/key/value"
-            )
-        return _nested(query, key, value, mask, triangle_bias, scale)
-    if is_nested(key) or is_nested(value):
-        raise ValueError("triangle_attention query, key, and value must all use the same NestedTensor layout")
-    if is_nested(mask) or is_nested(triangle_bias):
-        raise ValueError("triangle_attention dense query/key/value cannot use NestedTensor mask or triangle_bias")
-    require_no_forward_mode(_OPERATOR, query, key, value, triangle_bias)
-    return _dense(query, key, value, mask, triangle_bias, scale)
+    operands = {"query": query, "key": key, "value": value, "mask": mask, "triangle_bias": triangle_bias}
+    packed = {name for name, operand in operands.items() if operand is not None and is_nested(operand)}
+    pair_names = {"query", "key", "value"}
+    if packed & pair_names and not pair_names <= packed:
+        raise ValueError(_MIXED_QKV)
+    if not packed & pair_names:
+        if packed:
+            raise ValueError("triangle_attention dense query/key/value cannot use NestedTensor mask or triangle_bias")
+        require_no_forward_mode(_OPERATOR, query, key, value, triangle_bias)
+        return _dense(query, key, value, mask, triangle_bias, scale)
+    # a packed ragged batch: every optional operand that is given must be packed too
+    for name, message in _DENSE_OPTIONAL_WITH_PACKED.items():
+        if operands[name] is not None and name not in packed:
+            raise ValueError(message)
+    return _nested(query, key, value, mask, triangle_bias, scale)
+
+
+_MIXED_QKV = "triangle_attention query, key, and value must all use the same NestedTensor layout"
+_DENSE_OPTIONAL_WITH_PACKED = {
+    "mask": "triangle_attention mask must use the same NestedTensor layout as nested query/key/value",
+    "triangle_bias": "triangle_attention triangle_bias must use a compatible NestedTensor layout with nested "
+    "query/key/value",
+}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -128,34 +135,36 @@ def _require_bool_mask(mask: Optional[Tensor]) -> None:
         raise unsupported(_OPERATOR, "requires a bool keep-mask", mask_dtype=mask.dtype)
 
 
+def _right_aligned_broadcast(shape: Tuple[int, ...], target: Tuple[int, ...]) -> bool:
+    """Whether ``shape`` expands to ``target`` under the usual trailing-axis alignment."""
+    if len(shape) > len(target):
+        return False
+    padded = (1,) * (len(target) - len(shape)) + tuple(shape)
+    return all(own in (1, want) for own, want in zip(padded, target))
+
+
 def _check_dense_shapes(query, key, value, mask, triangle_bias) -> None:
-    if query.dim() < 4:
+    rank = query.dim()
+    if rank < 4:
         raise ValueError(
             "triangle_attention query must be (*prefix, rows, cols, num_heads, head_size) of rank at least 4, "
-            f"got rank {query.dim()}"
+            f"got rank {rank}"
         )
-    if key.shape != query.shape or value.shape != query.shape:
+    if not (tuple(key.shape) == tuple(value.shape) == tuple(query.shape)):
         raise ValueError("triangle_attention query, key, and value must have the same shape")
-    if mask is not None:
-        target = tuple(query.shape[:-2])
-        if mask.dim() > len(target) or any(
-            size not in (1, extent) for size, extent in zip(reversed(mask.shape), reversed(target))
-        ):
-            raise ValueError(
-                f"triangle_attention mask shape {tuple(mask.shape)} must broadcast to the query's "
-                f"(*prefix, rows, cols) = {target}"
-            )
+    prefix, (rows, cols, num_heads) = tuple(query.shape[:-4]), tuple(query.shape[-4:-1])
+    pair_shape = (*prefix, rows, cols)
+    if mask is not None and not _right_aligned_broadcast(tuple(mask.shape), pair_shape):
+        raise ValueError(
+            f"triangle_attention mask shape {tuple(mask.shape)} must broadcast to the query's "
+            f"(*prefix, rows, cols) = {pair_shape}"
+        )
     if triangle_bias is not None:
-        *prefix, rows, cols, num_heads, _head_size = query.shape
-        expected = (*prefix, "rows|1", num_heads, cols, cols)
-        shape = tuple(triangle_bias.shape)
-        if (
-            triangle_bias.dim() != query.dim()
-            or shape[: len(prefix)] != tuple(prefix)
-            or shape[len(prefix)] not in (1, rows)
-            or shape[len(prefix) + 1 :] != (num_heads, cols, cols)
-        ):
-            raise ValueError(f"triangle_attention triangle_bias shape {shape} must be {expected}")
+        got = tuple(triangle_bias.shape)
+        accepted = {(*prefix, groups, num_heads, cols, cols) for groups in (1, rows)}
+        if got not in accepted:
+            wanted = (*prefix, "rows|1", num_heads, cols, cols)
+            raise ValueError(f"triangle_attention triangle_bias shape {got} must be {wanted}")
 
 
 def _check_admission(query, key, value, mask, bias, what: str) -> None:
@@ -196,35 +205,31 @@ def _dense(query, key, value, mask, triangle_bias, scale):
         "a bool mask broadcastable to (*prefix, rows, cols), and a (*prefix, rows|1, num_heads, cols, cols) "
         "bias in the q/k/v dtype or float32",
     )
-    shape = query.shape
-    batchless = query.dim() == 4
-    prefixed = query.dim() > 5
+    lead_rank = query.dim() - 4  # axes in front of (rows, cols, num_heads, head_size)
 
-    def batched(tensor: Tensor) -> Tensor:
-        if batchless:
-            return tensor.unsqueeze(0)
-        return tensor.flatten(0, -5) if prefixed else tensor
+    def as_batch(tensor: Tensor, keep: int = 4) -> Tensor:
+        """Fold the leading axes of ``(*lead, <keep axes>)`` into one batch axis (a view where strides allow)."""
+        lead = tensor.dim() - keep
+        if lead == 1:
+            return tensor
+        return tensor.unsqueeze(0) if lead == 0 else tensor.flatten(0, lead - 1)
 
-    q5 = _unit_inner(batched(query))
-    k5 = q5 if key is query else _unit_inner(batched(key))
-    v5 = q5 if value is query else k5 if value is key else _unit_inner(batched(value))
-    batch, rows, cols, _heads, head_size = q5.shape
-    mask3 = None
-    if mask is not None:
-        mask3 = mask.expand(shape[:-2]).reshape(batch, rows, cols) if prefixed else mask.expand(shape[:-2])
-        if batchless:
-            mask3 = mask3.unsqueeze(0)
+    q5 = _unit_inner(as_batch(query))
+    # operands that are the same object stay the same object: the kernels then read one buffer
+    k5 = q5 if key is query else _unit_inner(as_batch(key))
+    v5 = q5 if value is query else k5 if value is key else _unit_inner(as_batch(value))
+    rows, cols, head_size = q5.shape[1], q5.shape[2], q5.shape[4]
+    mask3 = None if mask is None else as_batch(mask.expand(query.shape[:-2]), keep=2)
     bias5 = None
     if triangle_bias is not None:
-        bias5 = batched(triangle_bias).resolve_neg().resolve_conj().contiguous()
+        bias5 = as_batch(triangle_bias).resolve_neg().resolve_conj().contiguous()
         if bias5.element_size() == 2 and cols % 8 != 0:
             # 16-byte aligned bias rows (the TMA kernels need them): pad the key axis, then view the first `cols` keys
             bias5 = torch.nn.functional.pad(bias5, (0, -cols % 8))[..., :cols]
     scale = head_size**-0.5 if scale is None else float(scale)
     out = _function.apply(q5, k5, v5, mask3, bias5, scale, DenseGeometry(), _flags())
-    if batchless:
-        return out.squeeze(0)
-    return out.reshape(shape) if prefixed else out
+    # undoing the batch fold never needs a copy: it removes a unit axis or splits the leading one
+    return out if lead_rank == 1 else out.squeeze(0) if lead_rank == 0 else out.unflatten(0, tuple(query.shape[:lead_rank]))
 
 
 # ----------------------------------------------------------------------------------------------
@@ -232,40 +237,51 @@ def _dense(query, key, value, mask, triangle_bias, scale):
 # ----------------------------------------------------------------------------------------------
 
 
+def _packing_of(nested, ragged_axes: Tuple[int, ...], static_axes: Tuple[int, ...]) -> Optional[bool]:
+    """Classify how a ragged container packs its elements.
+
+    ``ragged_axes`` are the element axes that vary per sample in their canonical order (the last two are the pair
+    or query/key axes) and ``static_axes`` the remaining element axes in storage order.  Returns ``False`` when the
+    container packs exactly ``(*ragged_axes, *static_axes)``, ``True`` when it packs the same with the last two ragged
+    axes exchanged (the ending-node order), ``None`` for anything else.
+    """
+    found = (tuple(nested.ragged_dims), tuple(nested.packed_dim_order))
+    for exchanged in (False, True):
+        axes = ragged_axes[:-2] + (ragged_axes[-1], ragged_axes[-2]) if exchanged else ragged_axes
+        if found == (axes, axes + static_axes):
+            return exchanged
+    return None
+
+
 def _canonical_nested_qkv(operand: str, nested) -> Tuple[Tensor, bool]:
-    if not nested.batch_first or nested.dim() < 5:
+    rank = nested.dim()  # element rank plus the batch axis
+    if rank < 5 or not nested.batch_first:
         raise ValueError(f"triangle_attention nested {operand} elements must have shape (*prefix, N_i, N_i, H, D)")
-    prefix_rank = nested.dim() - 5
-    tail = (*range(prefix_rank), prefix_rank + 2, prefix_rank + 3)
-    ragged, order = tuple(nested.ragged_dims), tuple(nested.packed_dim_order)
-    canonical = ragged == (prefix_rank, prefix_rank + 1) and order == (prefix_rank, prefix_rank + 1, *tail)
-    transposed = ragged == (prefix_rank + 1, prefix_rank) and order == (prefix_rank + 1, prefix_rank, *tail)
-    if not canonical and not transposed:
+    p = rank - 5
+    transposed = _packing_of(nested, (p, p + 1), (*range(p), p + 2, p + 3))
+    if transposed is None:
         raise unsupported(
             _OPERATOR,
             f"requires explicit canonical or transposed (*prefix, N_i, N_i, H, D) nested {operand} packing",
-            ragged_dims=ragged,
-            packed_dim_order=order,
+            ragged_dims=tuple(nested.ragged_dims),
+            packed_dim_order=tuple(nested.packed_dim_order),
         )
     values = nested.concat
-    if values.dim() != prefix_rank + 3 or values.shape[-2] <= 0 or values.shape[-1] <= 0:
+    heads_and_channels = tuple(values.shape[-2:])
+    if values.dim() != p + 3 or min(heads_and_channels) <= 0:
         raise ValueError(f"triangle_attention nested {operand} must retain positive num_heads and head_size axes")
     return values, transposed
 
 
 def _broadcast_nested_prefix(values: Tensor, prefix_shape: Tuple[int, ...], tail_rank: int) -> Tensor:
-    own_prefix = tuple(values.shape[1 : values.dim() - tail_rank] if tail_rank else values.shape[1:])
-    message = "triangle_attention nested mask and bias static prefixes must broadcast to the query prefix"
-    try:
-        broadcast_prefix = torch.broadcast_shapes(own_prefix, prefix_shape)
-    except RuntimeError as error:
-        raise ValueError(message) from error
-    if tuple(broadcast_prefix) != tuple(prefix_shape):
-        raise ValueError(message)
-    tail = tuple(values.shape[-tail_rank:]) if tail_rank else ()
-    return values.reshape(values.shape[0], *((1,) * (len(prefix_shape) - len(own_prefix))), *own_prefix, *tail).expand(
-        values.shape[0], *prefix_shape, *tail
-    )
+    """Expand the static prefix axes of packed values ``(cells, *own_prefix, *tail)`` to ``prefix_shape``."""
+    split = values.dim() - tail_rank
+    cells, own, tail = values.shape[0], tuple(values.shape[1:split]), tuple(values.shape[split:])
+    wanted = tuple(prefix_shape)
+    if not _right_aligned_broadcast(own, wanted):
+        raise ValueError("triangle_attention nested mask and bias static prefixes must broadcast to the query prefix")
+    aligned = (1,) * (len(wanted) - len(own)) + own
+    return values.reshape(cells, *aligned, *tail).expand(cells, *wanted, *tail)
 
 
 def _boundaries(nested, level) -> list:
@@ -303,24 +319,22 @@ def _sample_lengths(operand: str, nested) -> Tuple[int, ...]:
 
 
 def _nested_mask(mask, prefix_shape, transposed: bool, lengths) -> Tensor:
-    if not mask.batch_first or mask.dim() < 3:
+    rank = mask.dim()
+    if rank < 3 or not mask.batch_first:
         raise ValueError("triangle_attention nested mask elements must have shape (*prefix, N_i, N_i)")
-    prefix_rank = mask.dim() - 3
-    tail = tuple(range(prefix_rank))
-    ragged, order = tuple(mask.ragged_dims), tuple(mask.packed_dim_order)
-    canonical = ragged == (prefix_rank, prefix_rank + 1) and order == (prefix_rank, prefix_rank + 1, *tail)
-    mask_transposed = ragged == (prefix_rank + 1, prefix_rank) and order == (prefix_rank + 1, prefix_rank, *tail)
-    if not canonical and not mask_transposed:
+    p = rank - 3
+    mask_transposed = _packing_of(mask, (p, p + 1), tuple(range(p)))
+    if mask_transposed is None:
         raise unsupported(
             _OPERATOR,
             "requires explicit canonical or transposed (*prefix, N_i, N_i) nested mask packing",
-            ragged_dims=ragged,
-            packed_dim_order=order,
+            ragged_dims=tuple(mask.ragged_dims),
+            packed_dim_order=tuple(mask.packed_dim_order),
         )
-    if mask_transposed != transposed:
+    if mask_transposed is not transposed:
         raise ValueError("triangle_attention nested mask must share q/k/v packed pair-axis orientation")
     values = mask.concat
-    if values.dim() != prefix_rank + 1:
+    if values.dim() != p + 1:
         raise ValueError("triangle_attention nested mask must have flattened square pair storage")
     _require_bool_mask(values)
     if _sample_lengths("mask", mask) != tuple(lengths):
@@ -336,30 +350,24 @@ def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[
     a per-sample permutation for transposed ones (triangle_attention.py:317-325, nested.py:325-335);
     here both are plain differentiable PyTorch views and one copy.
     """
-    if not triangle_bias.batch_first or triangle_bias.dim() < 5:
+    rank = triangle_bias.dim()
+    if rank < 5 or not triangle_bias.batch_first:
         raise ValueError(
             "triangle_attention nested triangle_bias elements must have shape (*prefix, rows|1, H, N_i, N_i)"
         )
-    prefix_rank = triangle_bias.dim() - 5
-    ragged, order = tuple(triangle_bias.ragged_dims), tuple(triangle_bias.packed_dim_order)
-    static_prefix = tuple(range(prefix_rank))
-    shared_tail = (*static_prefix, prefix_rank, prefix_rank + 1)
-    full_tail = (*static_prefix, prefix_rank + 1)
-    if ragged == (prefix_rank + 2, prefix_rank + 3) and order == (*ragged, *shared_tail):
-        shared, transposed = True, False
-    elif ragged == (prefix_rank + 3, prefix_rank + 2) and order == (*ragged, *shared_tail):
-        shared, transposed = True, True
-    elif ragged == (prefix_rank, prefix_rank + 2, prefix_rank + 3) and order == (*ragged, *full_tail):
-        shared, transposed = False, False
-    elif ragged == (prefix_rank, prefix_rank + 3, prefix_rank + 2) and order == (*ragged, *full_tail):
-        shared, transposed = False, True
-    else:
+    p = rank - 5
+    # element axes: p = group (rows|1), p + 1 = head, p + 2 = query, p + 3 = key.  A row-shared bias varies per sample
+    # in its query/key axes only; a per-row bias also in its group axis.
+    shared, transposed = True, _packing_of(triangle_bias, (p + 2, p + 3), (*range(p), p, p + 1))
+    if transposed is None:
+        shared, transposed = False, _packing_of(triangle_bias, (p, p + 2, p + 3), (*range(p), p + 1))
+    if transposed is None:
         raise unsupported(
             _OPERATOR,
             "requires literal dense-order nested triangle_bias elements with canonical or transposed shared/full "
             "pair-axis ragged dimensions",
-            ragged_dims=ragged,
-            packed_dim_order=order,
+            ragged_dims=tuple(triangle_bias.ragged_dims),
+            packed_dim_order=tuple(triangle_bias.packed_dim_order),
         )
     packed = triangle_bias.concat
     if shared and packed.shape[-2] != 1:
@@ -410,17 +418,17 @@ def _nested_bias(triangle_bias, num_heads: int, prefix_shape, lengths) -> Tuple[
 
 
 def _nested(query, key, value, mask, triangle_bias, scale):
-    query_values, transposed = _canonical_nested_qkv("query", query)
-    key_values, key_transposed = _canonical_nested_qkv("key", key)
-    value_values, value_transposed = _canonical_nested_qkv("value", value)
+    pair_operands = (("query", query), ("key", key), ("value", value))
+    unpacked = [_canonical_nested_qkv(name, operand) for name, operand in pair_operands]
+    (query_values, transposed), (key_values, _), (value_values, _) = unpacked
     require_no_forward_mode(
         _OPERATOR, query_values, key_values, value_values, None if triangle_bias is None else triangle_bias.concat
     )
-    if key_values.shape[1:] != query_values.shape[1:] or value_values.shape[1:] != query_values.shape[1:]:
+    if any(values.shape[1:] != query_values.shape[1:] for values, _ in unpacked[1:]):
         raise ValueError(
             "triangle_attention nested query, key, and value must share static prefix, num_heads, and head_size"
         )
-    if key_transposed != transposed or value_transposed != transposed:
+    if any(orientation is not transposed for _, orientation in unpacked[1:]):
         raise ValueError("triangle_attention nested query, key, and value must share packed pair-axis orientation")
     lengths = _sample_lengths("query", query)
     for operand, nested in (("key", key), ("value", value)):
