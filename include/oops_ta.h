@@ -197,6 +197,16 @@ uint64_t oops_ta_forward_static_capacity(void);
  */
 int oops_ta_device_status(int reset);
 
+/*
+ * Self-test of the bounded device-side wait.  Enqueues a one-CTA kernel whose only wait is on a barrier
+ * that nothing completes, with a limit of one millisecond: the wait gives up, the CTA tears down the way a
+ * compute kernel does after a wait that ran out, and the kernel returns by itself.  Afterwards
+ * oops_ta_device_status reports OOPS_TA_DEVICE_TIMEOUT until it is reset, and the tensor kernels of the
+ * forward pass return at once.  Meant for tests and for checking a deployment's status polling.
+ * No counterpart in the reference.
+ */
+int oops_ta_selftest_wait_limit(void* stream);
+
 /* Number of kernels the library has launched in this process (all streams). */
 uint64_t oops_ta_launch_count(void);
 

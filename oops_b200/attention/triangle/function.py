@@ -17,6 +17,7 @@ packed layout the reference documents in ``oops/attention/triangle/nested.py:
 
 from __future__ import annotations
 
+from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
@@ -132,6 +133,34 @@ class NestedGeometry:
         return bias.contiguous()
 
 
+_CHECK_DEVICE_STATUS = False
+
+
+@contextmanager
+def checked_device_status(enabled: bool = True):
+    """Inside the block every forward and reverse call ends by synchronising with the device and reading the
+    library's device-side status word; a kernel that gave up one of its bounded waits (its outputs are then
+    undefined) raises ``RuntimeError`` and the word is cleared.  Off by default because of the synchronisation:
+    production callers poll ``oops_b200.runtime.cabi.device_status()`` at a point where they synchronise anyway."""
+    global _CHECK_DEVICE_STATUS
+    previous, _CHECK_DEVICE_STATUS = _CHECK_DEVICE_STATUS, enabled
+    try:
+        yield
+    finally:
+        _CHECK_DEVICE_STATUS = previous
+
+
+def _raise_if_device_failed(what: str) -> None:
+    if not _CHECK_DEVICE_STATUS:
+        return
+    status = cabi.device_status(reset=True)
+    if status:
+        raise RuntimeError(
+            f"triangle_attention {what}: a kernel recorded device status {status} "
+            f"({cabi.library().oops_ta_status_string(status).decode()}); its results are undefined"
+        )
+
+
 def _current_stream_handle(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -196,6 +225,7 @@ def run_forward(
             )
             if status:
                 _raise_status(status, "forward")
+        _raise_if_device_failed("forward")
     return out, lse
 
 
@@ -251,6 +281,7 @@ def run_backward(
             )
             if status:
                 _raise_status(status, "backward")
+        _raise_if_device_failed("backward")
     return dq, dk, dv, dbias
 
 

@@ -18,7 +18,7 @@ from torch import Tensor
 from ...runtime import cabi, require_no_forward_mode, require_same_device, unsupported
 from ...runtime.nested_tensor import is_nested
 from . import function as _function
-from .function import DenseGeometry, NestedGeometry
+from .function import DenseGeometry, NestedGeometry, checked_device_status
 
 _OPERATOR = "triangle_attention"
 _DTYPES = (torch.float16, torch.bfloat16, torch.float32)
@@ -471,4 +471,4 @@ def _nested(query, key, value, mask, triangle_bias, scale):
     return query.packed_like(out.reshape(total_cells, *prefix_shape, num_heads, head_size))
 
 
-__all__ = ["triangle_attention", "layout_agnostic_kernels"]
+__all__ = ["triangle_attention", "layout_agnostic_kernels", "separate_reverse_kernels", "checked_device_status"]

@@ -48,9 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         src = CSRC / name
         obj = obj_dir / (src.stem + ".o")
         if force or _stale(obj, [src, *headers]):
-            extra = ["-DTA_PROFILE_WAITS"] if os.environ.get("OOPS_TA_PROFILE_WAITS") else []
-            extra += os.environ.get("OOPS_TA_EXTRA_NVCC_FLAGS", "").split()
-            cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             done = subprocess.run(cmd, capture_output=True, text=True)
             log = obj_dir / (src.stem + ".ptxas.log")
             log.write_text(done.stdout + done.stderr)

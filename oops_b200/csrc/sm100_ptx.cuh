@@ -60,33 +60,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // others stop waiting too.  Returns false if the wait was abandoned.
 constexpr uint64_t kWaitLimitNs = 250000000ull;  // 0.25 s
 
-#ifdef TA_PROFILE_WAITS
-#define TA_WAIT_SLOT(name) unsigned long long name = 0
-#define TA_WAIT_ARG(name) , &name
-#else
-#define TA_WAIT_SLOT(name)
-#define TA_WAIT_ARG(name)
-#endif
-
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned long long* waited = nullptr) {
-#ifdef TA_PROFILE_WAITS
-  const long long t0 = clock64();
-  struct Stop {
-    unsigned long long* w;
-    long long t0;
-    __device__ ~Stop() {
-      if (w) *w += (unsigned long long)(clock64() - t0);
-    }
-  } stop{waited, t0};
-#endif
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t start = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x7) == 0) {
       if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - start > kWaitLimitNs) {
+      if (globaltimer_ns() - start > limit_ns) {
         *abort_flag = 1;
         return false;
       }
@@ -273,6 +255,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+// 8-column load.
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(addr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -305,6 +294,36 @@ __device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
 __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return __fmul2_rn(a, b); }
+
+// fma with the result clamped to [0, 1] (a NaN or -inf input gives 0).
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+  float d;
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^(128 u + kExp2PolyLow) for a pair of u in [0, 1], computed on the FMA pipe instead of the special-function unit
+// (which serves 16 `ex2` per clock per SM and is the first pipe to saturate at head size 32).  The caller obtains u
+// from its exponent x with one saturating multiply-add, u = sat((x - low) / 128), which also clamps x to
+// [low, low + 128].  w = 128 u is split by the round-to-nearest of a large-constant add into an integer n and a
+// remainder f in [-1/2, 1/2]; 2^f is a degree-3 polynomial (relative error 7.5e-5, below the 16-bit rounding the
+// result gets before its MMA); n + low goes into the exponent field with one shift-add per element.
+constexpr int kExp2PolyLow = -120;  // results span 2^-120 .. 2^8: exponents above the running maximum by the lazy-rescale slack fit
+__device__ __forceinline__ f32x2 ex2_poly_unit(f32x2 u) {
+  constexpr float magic = 12582912.f + float(kExp2PolyLow);  // 1.5 * 2^23 + low: the sum's low mantissa bits hold n + low
+  const f32x2 scale128 = pack2(128.f, 128.f), magic2 = pack2(magic, magic);
+  const f32x2 r = fma2(u, scale128, magic2);
+  const f32x2 minus_n = fma2(r, pack2(-1.f, -1.f), magic2);
+  const f32x2 f = fma2(u, scale128, minus_n);
+  f32x2 poly = fma2(f, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
+  poly = fma2(poly, f, pack2(0.6932609677f, 0.6932609677f));
+  poly = fma2(poly, f, pack2(0.9999280572f, 0.9999280572f));
+  float r_lo, r_hi, p_lo, p_hi;
+  unpack2(r, r_lo, r_hi);
+  unpack2(poly, p_lo, p_hi);
+  return pack2(__int_as_float(__float_as_int(p_lo) + (__float_as_int(r_lo) << 23)),
+               __int_as_float(__float_as_int(p_hi) + (__float_as_int(r_hi) << 23)));
+}
 
 template <typename T>
 struct Half2;

@@ -176,6 +176,13 @@ int oops_ta_device_status(int reset) {
   return forward ? forward : backward;
 }
 
+int oops_ta_selftest_wait_limit(void* stream) {
+  const int status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  return wait_limit_selftest(reinterpret_cast<cudaStream_t>(stream));
+}
+
 uint64_t oops_ta_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -44,6 +44,8 @@ int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oop
 // Read (and optionally clear) the device-side status words of the two tcgen05 translation units;
 // both synchronise with the device.
 int forward_device_status(int reset);
+// Launches the bounded-wait self-test kernel of the forward translation unit (its wait runs out after 1 ms).
+int wait_limit_selftest(cudaStream_t stream);
 int backward_device_status(int reset);
 
 }  // namespace oops_ta

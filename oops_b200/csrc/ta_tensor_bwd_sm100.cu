@@ -31,11 +31,8 @@ constexpr int kTilesPerCta = 1;                          // dQ and dK/dV kernels
 constexpr int kElemWarps = 8 * kTilesPerCta;             // two warpgroups per tile
 constexpr int kThreads = (kElemWarps + (kTilesPerCta == 2 ? 3 : 2)) * 32;
 constexpr int kCtasPerSm = kTilesPerCta == 2 ? 1 : 2;
-constexpr int kDbKeys = 64;                              // shared-bias kernel: keys of a CTA's tile (64 or 128)
-constexpr int kDbElemWarps = 4 * (kDbKeys / 32);         // one warpgroup per 32 keys
+constexpr int kDbElemWarps = 16;                         // shared-bias kernel: one warpgroup per 32 of the tile's 128 keys
 constexpr int kDbThreads = (kDbElemWarps + 2) * 32;
-constexpr int kDbCtasPerSm = kDbKeys == 64 ? 2 : 1;
-constexpr int kDbKvTile = kDbKeys * kHeadDim * 2;        // K or V rows of the tile
 constexpr int kStep = 64;                               // streamed keys (dQ) or queries (dK/dV) per step
 constexpr int kBigTile = kTile * kHeadDim * 2;          // 8 KiB: 128 x 32 tile
 constexpr int kSmallTile = kStep * kHeadDim * 2;        // 4 KiB: 64 x 32 tile
@@ -149,17 +146,6 @@ __device__ __forceinline__ bool pair_vec_ok(const oops_ta_pair& t) {
 constexpr int kProducerWarp = kElemWarps, kMmaWarp = kElemWarps + 1, kAccWarp = kElemWarps + 2;
 constexpr int kDbProducerWarp = kDbElemWarps, kDbMmaWarp = kDbElemWarps + 1;
 
-#ifdef TA_PROFILE_WAITS
-// dK/dV kernel, clocks summed over warpgroups (thread 0 of each): 0 sd_full, 1 bias_full, 2 pds_done, 3 stats+named barrier,
-// 4 compute, 5 store+arrive, 6 loop total, 7 warpgroup count; MMA thread: 8 sd_free, 9 pds_full, 10 qd_full, 11 loop total,
-// 12 CTA count; producer: 13 qd_empty, 14 bias_empty
-__device__ unsigned long long g_bwd_clk[48];
-#define TB_ADD(slot, value) atomicAdd(&g_bwd_clk[slot], (unsigned long long)(value))
-#define TB_CLOCK(name) const long long name = clock64()
-#else
-#define TB_ADD(slot, value)
-#define TB_CLOCK(name)
-#endif
 constexpr int kMaxKeepWords = 512;  // keep-bit table: one bit per key column, cols <= 16384
 
 // Eight columns of the reverse-pass element math on packed f32 pairs:
@@ -479,13 +465,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       db_vec = P.db_sk == 1 && (reinterpret_cast<uintptr_t>(db_row) & 15) == 0;
     }
     bool ok = true;
-#ifdef TA_PROFILE_WAITS
-    uint32_t qc[6] = {0, 0, 0, 0, 0, 0};
-    const long long q_loop_start = clock64();
-#endif
 
     for (int j = 0; j < KS && ok; ++j) {
-      TB_CLOCK(qk0);
       uint32_t my_bits = 0xffffffffu;
       bool step_all_kept = true;
       if (has_bits) {
@@ -510,7 +491,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       }
       ok = mbar_wait(bar(DqSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
-      TB_CLOCK(qk1);
       tc_fence_after_sync();
       uint32_t sraw[32], draw[32];
       tmem_ld32(tile_t + half * 32, sraw);
@@ -518,9 +498,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::sd_free + w));
-      TB_CLOCK(qk2);
       const int slot = w * 2 + (j & 1);
-      TB_CLOCK(qk3);
       const uint8_t* bias_row = smem_gen + DqSmem::bias + slot * kBiasStep + t * 128 + (((t & 7) ^ (half * 4)) << 4);
       uint32_t packed[16];
       const int key0 = j * kStep + half * 32;
@@ -551,30 +529,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
         }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DqSmem::bias_empty + slot));
-      TB_CLOCK(qk4);
       if (j > 0) {
         // the dQ product of the previous step must have finished reading the dS columns
         ok = mbar_wait(bar(DqSmem::ds_done + w), (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
       }
-      TB_CLOCK(qk5);
       tmem_st16(tile_t + kDsCol + half * 16, packed);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::ds_full + w));
-#ifdef TA_PROFILE_WAITS
-      TB_CLOCK(qk6);
-      qc[0] += uint32_t(qk1 - qk0); qc[1] += uint32_t(qk2 - qk1); qc[2] += uint32_t(qk3 - qk2); qc[3] += uint32_t(qk4 - qk3);
-      qc[4] += uint32_t(qk5 - qk4); qc[5] += uint32_t(qk6 - qk5);
-#endif
     }
-#ifdef TA_PROFILE_WAITS
-    if (t == 0) {
-      for (int i = 0; i < 6; ++i) TB_ADD(20 + i, qc[i]);
-      TB_ADD(26, clock64() - q_loop_start); TB_ADD(27, 1);
-    }
-#endif
 
     if (ok) ok = mbar_wait(bar(DqSmem::dq_done + w), 0, abort_flag);
     if (ok && half == 0) {
@@ -695,11 +660,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
         tma_load_5d(smem_base + DkvSmem::k + w * kBigTile, &P.map_k, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
         tma_load_5d(smem_base + DkvSmem::v + w * kBigTile, &P.map_v, bar(DkvSmem::kv_full + w), 0, h, k0 + w * kTile, r, b);
       }
-      TA_WAIT_SLOT(wq); TA_WAIT_SLOT(wb);
-      TB_CLOCK(p0);
       for (int j = 0; j < QS && ok; ++j) {
         const int st = j % kRing, round = j / kRing;
-        if (j >= kRing) ok = mbar_wait(bar(DkvSmem::qd_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wq));
+        if (j >= kRing) ok = mbar_wait(bar(DkvSmem::qd_empty + st), (round - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_expect_tx(bar(DkvSmem::qd_full + st), 2 * kSmallTile);
         const uint32_t dst = smem_base + DkvSmem::qd + st * 2 * kSmallTile;
@@ -708,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
         if (HAS_BIAS) {
           for (int w = 0; w < n_tiles && ok; ++w) {
             const int slot = w * 2 + (j & 1);
-            if (j >= 2) ok = mbar_wait(bar(DkvSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag TA_WAIT_ARG(wb));
+            if (j >= 2) ok = mbar_wait(bar(DkvSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
             if (!ok) break;
             mbar_expect_tx(bar(DkvSmem::bias_full + slot), kBiasStep);
             // transposed bias: inner axis = query, outer axis = key
@@ -717,9 +680,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
           }
         }
       }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(13, wq); TB_ADD(14, wb); TB_ADD(15, clock64() - p0);
-#endif
     }
   } else if (warp == kMmaWarp || (kTilesPerCta == 2 && warp == kAccWarp)) {
     // One tile per CTA: one thread issues everything in the order the events arrive (scores of step j+1 when the
@@ -767,10 +727,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
         if (j == QS - 1) mma_commit(bar(DkvSmem::done + w));
         if (w == n_tiles - 1) mma_commit(bar(DkvSmem::qd_empty + st));
       };
-      TA_WAIT_SLOT(wf); TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wq);
-#ifdef TA_PROFILE_WAITS
-      long long t_scores = 0, t_acc = 0;
-#endif
       if (do_scores) {
         for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(DkvSmem::kv_full + w), 0, abort_flag);
         if (ok) ok = mbar_wait(bar(DkvSmem::qd_full), 0, abort_flag);
@@ -779,39 +735,26 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
           for (int w = 0; w < n_tiles; ++w) issue_scores(0, w);
         }
       }
-      TB_CLOCK(m0);
       for (int j = 0; j < QS && ok; ++j) {
         if (do_scores && j + 1 < QS) {
-          ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+          ok = mbar_wait(bar(DkvSmem::qd_full + (j + 1) % kRing), ((j + 1) / kRing) & 1, abort_flag);
           for (int w = 0; w < n_tiles && ok; ++w) {
-            ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag TA_WAIT_ARG(wf));
+            ok = mbar_wait(bar(DkvSmem::sd_free + w), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
-            TB_CLOCK(i0);
             issue_scores(j + 1, w);
-#ifdef TA_PROFILE_WAITS
-            t_scores += clock64() - i0;
-#endif
           }
         }
         if (do_acc && ok) {
-          if (!do_scores) ok = mbar_wait(bar(DkvSmem::qd_full + j % kRing), (j / kRing) & 1, abort_flag TA_WAIT_ARG(wq));
+          if (!do_scores) ok = mbar_wait(bar(DkvSmem::qd_full + j % kRing), (j / kRing) & 1, abort_flag);
           for (int w = 0; w < n_tiles && ok; ++w) {
-            ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+            ok = mbar_wait(bar(DkvSmem::pds_full + w), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
-            TB_CLOCK(i1);
             issue_acc(j, w);
-#ifdef TA_PROFILE_WAITS
-            t_acc += clock64() - i1;
-#endif
           }
         }
       }
-#ifdef TA_PROFILE_WAITS
-      if (do_scores) { TB_ADD(6, t_scores); TB_ADD(8, wf); TB_ADD(10, wq); TB_ADD(11, clock64() - m0); TB_ADD(12, 1); }
-      if (do_acc) { TB_ADD(5, t_acc); TB_ADD(9, wp); TB_ADD(18, clock64() - m0); }
-#endif
     }
   } else if (warp < kElemWarps && (warp >> 3) < n_tiles) {
     const int w = warp >> 3;           // key tile
@@ -827,9 +770,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
     const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
     bool ok = true;
 
-#ifdef TA_PROFILE_WAITS
-    const long long loop_start = clock64();
-#endif
     // Row statistics of the step's 32 queries of this warpgroup's half: every warp keeps its own copy in shared
     // memory (no cross-warp barrier): lane i fetches -lse*log2e and -delta of query i one step ahead.
     // The loaded words are not touched until the next step (any arithmetic on them here would wait for the load).
@@ -844,24 +784,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
     };
     float nl_next, nd_next;
     fetch_stats(0, nl_next, nd_next);
-#ifdef TA_PROFILE_WAITS
-    uint32_t pc[6] = {0, 0, 0, 0, 0, 0};
-#endif
     for (int j = 0; j < QS && ok; ++j) {
-      TB_CLOCK(tk0);
       float* stats = reinterpret_cast<float*>(smem_gen + DkvSmem::stats + (warp * 2 + (j & 1)) * 256);
       stats[lane] = -nl_next * kLog2e;
       stats[32 + lane] = -nd_next;
       fetch_stats(j + 1, nl_next, nd_next);
       __syncwarp();
-      TB_CLOCK(tk1);
       ok = mbar_wait(bar(DkvSmem::sd_full + w), j & 1, abort_flag);
       if (!ok) break;
-      TB_CLOCK(tk2);
       tc_fence_after_sync();
       const int slot = w * 2 + (j & 1);
-      TB_CLOCK(tk3);
-      TB_CLOCK(tk4);
       const uint8_t* bias_row = smem_gen + DkvSmem::bias + slot * kBiasStep + t * 128 + (((t & 7) ^ (half * 4)) << 4);
       uint32_t p_packed[16], ds_packed[16];
       // two rounds of 16 queries keep the live registers low; the score columns are released after the second load
@@ -901,31 +833,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
         }
       }
       if (HAS_BIAS) mbar_arrive_warp(bar(DkvSmem::bias_empty + slot));
-      TB_CLOCK(tk5);
       if (j > 0) {
         ok = mbar_wait(bar(DkvSmem::pds_done + w), (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
       }
-      TB_CLOCK(tk6);
       tmem_st16(tile_t + kPCol + half * 16, p_packed);
       tmem_st16(tile_t + kDsCol + half * 16, ds_packed);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DkvSmem::pds_full + w));
-#ifdef TA_PROFILE_WAITS
-      TB_CLOCK(tk7);
-      pc[3] += uint32_t(tk1 - tk0); pc[0] += uint32_t(tk2 - tk1); pc[1] += uint32_t(tk4 - tk3);
-      pc[4] += uint32_t((tk3 - tk2) + (tk5 - tk4)); pc[2] += uint32_t(tk6 - tk5); pc[5] += uint32_t(tk7 - tk6);
-#endif
     }
-#ifdef TA_PROFILE_WAITS
-    if (t == 0) {
-      TB_ADD(3, pc[3]); TB_ADD(0, pc[0]); TB_ADD(1, pc[1]); TB_ADD(4, pc[4]); TB_ADD(2, pc[2]); TB_ADD(16, pc[5]);
-      TB_ADD(17, clock64() - loop_start);
-      TB_ADD(7, 1);
-    }
-#endif
 
     if (ok) ok = mbar_wait(bar(DkvSmem::done + w), 0, abort_flag);
     if (ok) {
@@ -1140,13 +1058,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
       bool ok = true;
-#ifdef TA_PROFILE_WAITS
-      long long f_wait = 0, f_issue = 0;
-      const long long f_start = clock64();
-#endif
       int kt = 0, qi = 0;
       for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-        TB_CLOCK(f0);
         const int qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok && qi == 0) {
@@ -1156,7 +1069,6 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (ok && s > 0) ok = mbar_wait(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        TB_CLOCK(f1);
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);
         const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);
         const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);
@@ -1168,13 +1080,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           mma_ss(tmem_base + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
         mma_commit(bar(FSmem::sd_full));
-#ifdef TA_PROFILE_WAITS
-        f_wait += f1 - f0; f_issue += clock64() - f1;
-#endif
       }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(36, f_wait); TB_ADD(37, f_issue); TB_ADD(38, clock64() - f_start); TB_ADD(39, steps);
-#endif
     }
   } else if (warp == kFAccWarp) {
     if (lane == 0) {
@@ -1182,13 +1088,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       constexpr uint32_t idesc_t = instr_desc(fmt, 1, 1, kTile, kHeadDim);  // A = image^T (M = keys), B MN-major
       constexpr uint32_t idesc_q = instr_desc(fmt, 0, 1, kTile, kHeadDim);  // A = image (M = queries), B MN-major
       bool ok = true;
-#ifdef TA_PROFILE_WAITS
-      long long g_wait = 0, g_issue = 0;
-      const long long g_start = clock64();
-#endif
       int kt = 0, qi = 0;
       for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-        TB_CLOCK(g0);
         const int qs = s % 3, ks = kt & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
@@ -1197,7 +1098,6 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (ok && qi == 0 && kt > 0) ok = mbar_wait(bar(FSmem::dkv_free), (kt - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        TB_CLOCK(g1);
         const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss + (s & 1) * kFImage;
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);     // MN-major B
         const uint64_t ddesc = smem_desc(smem_base + FSmem::dout + qs * kBigTile, 16, 512, kSwizzle64B);  // MN-major B
@@ -1218,13 +1118,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         mma_commit(bar(FSmem::pds_done + (s & 1)));
         mma_commit(bar(FSmem::qd_empty + qs));
         if (qi == nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
-#ifdef TA_PROFILE_WAITS
-        g_wait += g1 - g0; g_issue += clock64() - g1;
-#endif
       }
-#ifdef TA_PROFILE_WAITS
-      TB_ADD(40, g_wait); TB_ADD(41, g_issue); TB_ADD(42, clock64() - g_start);
-#endif
     }
   } else if (warp < 16) {
     const int wg = warp >> 2;  // 32 of the step's 128 keys
@@ -1272,17 +1166,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     float lse_next, delta_next;
     fetch_stats(0, 0, lse_next, delta_next);
     bool ok = true;
-#ifdef TA_PROFILE_WAITS
-    uint32_t wc[4] = {0, 0, 0, 0}, wx[3] = {0, 0, 0}, wy[2] = {0, 0};
-    const long long w_start = clock64();
-#endif
 
     // bias row of this thread's query in the staging tile: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
     const uint8_t* bias_row = smem_gen + FSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
 
     int kt = 0, qi = 0;
     for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-      TB_CLOCK(w0);
       const int buf = s & 1;
       const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
       fetch_stats(s + 1, qi + 1 == nq ? 0 : qi + 1, lse_next, delta_next);
@@ -1291,13 +1180,9 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       // The step's bias words go to registers at once and the staging tile is handed back, so that the next
       // tile's copy runs under this step's arithmetic.
       uint4 bias_words[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-      TB_CLOCK(wA);
       if (HAS_BIAS) {
         ok = mbar_wait(bar(FSmem::bias_full), s & 1, abort_flag);
         if (!ok) break;
-#ifdef TA_PROFILE_WAITS
-        wy[0] += uint32_t(wA - w0); wy[1] += uint32_t(clock64() - wA);
-#endif
 #pragma unroll
         for (int c = 0; c < 4; ++c) bias_words[c] = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, c));
         // the loads must have returned before the tile is handed back (the copy of the next tile may land at once)
@@ -1318,17 +1203,11 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         fence_proxy_async_smem();
         mbar_arrive_warp(bar(FSmem::k_ready + ks));
       }
-      TB_CLOCK(w0a);
       // this step's dS image was last read by the products of step s - 2, the P image by the dV products of s - 1
       if (s >= 2) ok = mbar_wait(bar(FSmem::pds_done + buf), ((s >> 1) - 1) & 1, abort_flag);
-      TB_CLOCK(w0b);
       if (ok) ok = mbar_wait(bar(FSmem::sd_full), s & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      TB_CLOCK(w1);
-#ifdef TA_PROFILE_WAITS
-      wx[0] += uint32_t(w0a - w0); wx[1] += uint32_t(w0b - w0a); wx[2] += uint32_t(w1 - w0b);
-#endif
       // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
       const int row_at = (wg >> 1) * 16384 + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
       uint8_t* p_row = smem_gen + FSmem::ps + row_at;
@@ -1371,7 +1250,6 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
             make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
-      TB_CLOCK(w2);
       if (qi == 0 && s > 0) {
         // a new key tile: dK and dV of the previous one are complete once the products of step s - 1 are
         ok = mbar_wait(bar(FSmem::pds_done + ((s - 1) & 1)), ((s - 1) >> 1) & 1, abort_flag);
@@ -1379,20 +1257,9 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         tc_fence_after_sync();
         store_key_tile(kt - 1);
       }
-      TB_CLOCK(w3);
       fence_proxy_async_smem();
       mbar_arrive_warp(bar(FSmem::pds_full + buf));
-#ifdef TA_PROFILE_WAITS
-      wc[0] += uint32_t(w1 - w0); wc[1] += uint32_t(w2 - w1); wc[2] += uint32_t(w3 - w2); wc[3] += uint32_t(clock64() - w3);
-#endif
     }
-#ifdef TA_PROFILE_WAITS
-    if (t == 0) {
-      TB_ADD(43, wc[0]); TB_ADD(44, wc[1]); TB_ADD(45, wc[2]); TB_ADD(46, wc[3]); TB_ADD(47, clock64() - w_start);
-      TB_ADD(32, wx[0]); TB_ADD(33, wx[1]); TB_ADD(34, wx[2]); TB_ADD(30, wy[0]); TB_ADD(31, wy[1]);
-      TB_ADD(35, steps);
-    }
-#endif
 
     // every product has finished when the products of the last two steps have
     if (ok && steps > 1) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 2) & 1)), ((steps - 2) >> 1) & 1, abort_flag);
@@ -1448,13 +1315,31 @@ __global__ void reduce_pair_parts_kernel(const float* parts, int groups, oops_ta
 // ---------------------------------------------------------------------------------------------
 // shared-bias gradient kernel
 // ---------------------------------------------------------------------------------------------
+// dBias[b, h, q, k] = sum over rows r of dS[b, r, h, q, k].  The sum runs over the rows, so this kernel's loop nest has
+// the rows innermost: a CTA owns one 128-query x 128-key tile of one (batch, head) and walks the rows of its part.
+// Per row the tensor core produces S = Q K^T and dP = dO V^T (two 128 x 128 x 32 products, full-rate N = 128
+// instructions, double-buffered in all 512 tensor-memory columns) and the sixteen element-wise warps (a thread owns
+// one query and 32 of the tile's keys) add dS into f32 registers.  Everything that does not depend on the row stays
+// in registers for the whole kernel: the thread's 32 bias values, already multiplied by log2(e), and the running
+// sums.  Per logit the loop then costs one packed add (bias - lse), one packed multiply-add (exponent), `ex2`, one
+// packed add (dP - delta) and one packed multiply-add (sum += P (dP - delta)).  A compile-time share of the `ex2`
+// runs as a polynomial on the FMA pipe.  With enough tiles to fill the SMs there is a single part and the CTA stores
+// the final 16-bit gradient itself; small problems split the rows into parts whose f32 planes a last kernel adds in a
+// fixed order (no atomics, bitwise reproducible either way).
 
-constexpr int kDbRing = 3;
+constexpr int kDbRing = 4;
+constexpr int kDbStage = 4 * kBigTile;  // Q | dO | K | V of one row: 128 x 32 each
+#ifndef TA_DB_POLY_EVERY
+#define TA_DB_POLY_EVERY 0
+#endif
+#ifndef TA_DB_VARIANT
+#define TA_DB_VARIANT 0
+#endif
+constexpr int kDbPolyEvery = TA_DB_POLY_EVERY;  // every n-th pair of a thread's logits takes the polynomial exp2 (0: none)
 struct DbSmem {
-  static constexpr int bias = 0;                                // 128 queries x kDbKeys (64-key boxes)
-  static constexpr int ring = bias + (kDbKeys / 64) * kBiasStep;      // [kDbRing] Q | dO (8 KiB each) | K | V
-  static constexpr int stage = 2 * kBigTile + 2 * kDbKvTile;
-  static constexpr int bars = ring + kDbRing * stage;
+  static constexpr int bias = 0;                         // 128 queries x 128 keys as two 64-key boxes (prologue only)
+  static constexpr int ring = bias + 2 * kBiasStep;      // [kDbRing] stages
+  static constexpr int bars = ring + kDbRing * kDbStage;
   static constexpr int bias_full = 0;
   static constexpr int row_full = 1;                     // [kDbRing]
   static constexpr int row_empty = row_full + kDbRing;   // [kDbRing]
@@ -1466,21 +1351,32 @@ struct DbSmem {
   static constexpr int total = abort_flag + 4;
 };
 constexpr int kDbSmemBytes = DbSmem::total + 1024;
+static_assert(kDbSmemBytes <= 232448, "shared-bias kernel: shared memory over the per-CTA limit");
 
 struct DbParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
-  float* parts;  // [parts][batch][heads][cols][cols] f32
+  float* parts;  // [parts][batch][heads][cols][cols] f32 (num_parts > 1)
+  void* dbias;   // final gradient in the bias type (num_parts == 1)
+  int64_t db_sb, db_sh, db_sq, db_sk;
   const float* lse;
   const float* delta;
   const uint8_t* mask;
   int64_t m_sb, m_sr, m_sc;
   int batch, rows, cols, heads;
-  int tiles, k_tiles, num_parts, rows_per_part;
+  int tiles, num_parts, rows_per_part;
   float scale;
 };
 
+#ifdef TA_PROFILE_DB
+__device__ unsigned long long g_db_clk[16];
+#define DB_CLK(name) const long long name = clock64()
+#define DB_ADD(slot, v) do { if (lane == 0) atomicAdd(&g_db_clk[slot], (unsigned long long)(v)); } while (0)
+#else
+#define DB_CLK(name)
+#define DB_ADD(slot, v)
+#endif
 template <typename T>
-__global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
+__global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -1491,8 +1387,8 @@ __global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
-  const int kt = idx % P.k_tiles;
-  idx /= P.k_tiles;
+  const int kt = idx % P.tiles;
+  idx /= P.tiles;
   const int qt = idx % P.tiles;
   idx /= P.tiles;
   const int h = idx % P.heads;
@@ -1518,7 +1414,7 @@ __global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(
     fence_barrier_init();
   }
   if (warp == kDbMmaWarp) {
-    tmem_alloc(smem_base + DbSmem::tmem_slot, 4 * kDbKeys);
+    tmem_alloc(smem_base + DbSmem::tmem_slot, 512);
     tmem_relinquish();
     tc_fence_before_sync();
   }
@@ -1529,26 +1425,25 @@ __global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(
   if (warp == kDbProducerWarp) {
     if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(bar(DbSmem::bias_full), (kDbKeys / 64) * kBiasStep);
-      for (int box = 0; box < kDbKeys / 64; ++box)
-        tma_load_5d(smem_base + DbSmem::bias + box * kBiasStep, &P.map_bias, bar(DbSmem::bias_full), kt * kDbKeys + box * 64,
+      mbar_expect_tx(bar(DbSmem::bias_full), 2 * kBiasStep);
+      for (int box = 0; box < 2; ++box)
+        tma_load_5d(smem_base + DbSmem::bias + box * kBiasStep, &P.map_bias, bar(DbSmem::bias_full), kt * kTile + box * 64,
                     qt * kTile, h, 0, b);
       for (int i = 0; i < n_rows && ok; ++i) {
         const int st = i % kDbRing, round = i / kDbRing, r = row_lo + i;
         if (i >= kDbRing) ok = mbar_wait(bar(DbSmem::row_empty + st), (round - 1) & 1, abort_flag);
         if (!ok) break;
-        mbar_expect_tx(bar(DbSmem::row_full + st), DbSmem::stage);
-        const uint32_t dst = smem_base + DbSmem::ring + st * DbSmem::stage;
+        mbar_expect_tx(bar(DbSmem::row_full + st), kDbStage);
+        const uint32_t dst = smem_base + DbSmem::ring + st * kDbStage;
         tma_load_5d(dst, &P.map_q, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
         tma_load_5d(dst + kBigTile, &P.map_dout, bar(DbSmem::row_full + st), 0, h, qt * kTile, r, b);
-        tma_load_5d(dst + 2 * kBigTile, &P.map_k, bar(DbSmem::row_full + st), 0, h, kt * kDbKeys, r, b);
-        tma_load_5d(dst + 2 * kBigTile + kDbKvTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kDbKeys, r, b);
+        tma_load_5d(dst + 2 * kBigTile, &P.map_k, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
+        tma_load_5d(dst + 3 * kBigTile, &P.map_v, bar(DbSmem::row_full + st), 0, h, kt * kTile, r, b);
       }
     }
   } else if (warp == kDbMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t fmt = Half2<T>::kFormat;
-      constexpr uint32_t idesc = instr_desc(fmt, 0, 0, kTile, kDbKeys);
+      constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
       bool ok = true;
       for (int i = 0; i < n_rows && ok; ++i) {
         const int st = i % kDbRing, buf = i & 1;
@@ -1556,37 +1451,59 @@ __global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(
         if (ok && i >= 2) ok = mbar_wait(bar(DbSmem::sd_free + buf), ((i >> 1) - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t base = smem_base + DbSmem::ring + st * DbSmem::stage;
+        const uint32_t base = smem_base + DbSmem::ring + st * kDbStage;
         const uint64_t qdesc = smem_desc(base, 16, 512, kSwizzle64B);
         const uint64_t ddesc = smem_desc(base + kBigTile, 16, 512, kSwizzle64B);
         const uint64_t kdesc = smem_desc(base + 2 * kBigTile, 16, 512, kSwizzle64B);
-        const uint64_t vdesc = smem_desc(base + 2 * kBigTile + kDbKvTile, 16, 512, kSwizzle64B);
-        const uint32_t s_t = tmem_base + buf * 2 * kDbKeys;
+        const uint64_t vdesc = smem_desc(base + 3 * kBigTile, 16, 512, kSwizzle64B);
+        const uint32_t s_t = tmem_base + buf * 2 * kTile;
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           mma_ss(s_t, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          mma_ss(s_t + kDbKeys, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+          mma_ss(s_t + kTile, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
         mma_commit(bar(DbSmem::sd_full + buf));
         mma_commit(bar(DbSmem::row_empty + st));
       }
     }
   } else if (warp < kDbElemWarps) {
-    const int wg = warp >> 2;  // 32 of the tile's keys
+    const int wg = warp >> 2;  // 32 of the tile's 128 keys
     const int t = tid & (kTile - 1);
     const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
     const int q_index = qt * kTile + t;
     const bool q_valid = q_index < P.cols;
-    const int key_base = kt * kDbKeys + wg * 32;
+    const int key_base = kt * kTile + wg * 32;
     const float scale = P.scale;
+    constexpr float kUnit = 1.f / 128.f, kUnitShift = float(-kExp2PolyLow) / 128.f;
+    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e);
+    const float c_unit = scale * kLog2e * kUnit;
+
+    // The thread's bias values, times log2(e), for the whole kernel.
+    bool ok = mbar_wait(bar(DbSmem::bias_full), 0, abort_flag);
+#if TA_DB_VARIANT == 1
+    const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
+    const f32x2 log2e2 = pack2(kLog2e, kLog2e);
+#else
+    f32x2 bias2[16];
+    {
+      const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
+      const f32x2 log2e2 = pack2(kLog2e, kLog2e);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (ok) v = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, c));
+        bias2[4 * c + 0] = mul2(Half2<T>::widen(v.x), log2e2);
+        bias2[4 * c + 1] = mul2(Half2<T>::widen(v.y), log2e2);
+        bias2[4 * c + 2] = mul2(Half2<T>::widen(v.z), log2e2);
+        bias2[4 * c + 3] = mul2(Half2<T>::widen(v.w), log2e2);
+      }
+    }
+#endif
     f32x2 acc2[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc2[i] = pack2(0.f, 0.f);
-    const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
-    bool ok = mbar_wait(bar(DbSmem::bias_full), 0, abort_flag);
-    // bias tile: two 64-key boxes; this warpgroup reads 16-byte chunks (wg & 1) * 4 .. + 3 of box (wg >> 1)
-    const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128;
+
     const bool need_bits = has_mask || key_base + 32 > P.cols;
     const int64_t stat_stride = int64_t(P.heads) * P.cols;
     const int64_t stat_first = ((int64_t(b) * P.rows + row_lo) * P.heads + h) * P.cols + q_index;
@@ -1609,65 +1526,147 @@ __global__ void __launch_bounds__(kDbThreads, kDbCtasPerSm) ta_bwd_dbias_kernel(
         }
       }
     };
-    float neg_lse2, delta, next_lse, next_dl;
+    float next_lse, next_dl;
     uint32_t next_keep;
     load_stats(0, next_lse, next_dl, next_keep);
 
     for (int i = 0; i < n_rows && ok; ++i) {
       const int buf = i & 1;
-      neg_lse2 = -next_lse * kLog2e;
-      delta = next_dl;
+      const float neg_lse2 = -next_lse * kLog2e, neg_delta = -next_dl;
       const bool keep_lane = next_keep != 0;
       load_stats(i + 1, next_lse, next_dl, next_keep);
       const uint32_t bits = need_bits ? __ballot_sync(0xffffffffu, keep_lane) : 0xffffffffu;
+      const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
+      const float nl_unit = fmaf(neg_lse2, kUnit, kUnitShift);
+      DB_CLK(c0);
       ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kDbKeys + wg * 32;
-      const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(-delta, -delta);
-      const f32x2 nl2[4] = {nl1, nl1, nl1, nl1}, nd2[4] = {nd1, nd1, nd1, nd1};
+      DB_CLK(c1);
+      DB_ADD(0, c1 - c0);
+      const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
+#if TA_DB_VARIANT == 1
+      // bias words from the staging tile (it stays resident); the tensor-memory loads of the next eight columns are
+      // in flight while the current eight are worked on
+      auto work8 = [&](int round, const uint32_t (&sraw)[8], const uint32_t (&draw)[8]) {
+        const uint4 bw4 = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, round));
+        const uint32_t bw[4] = {bw4.x, bw4.y, bw4.z, bw4.w};
 #pragma unroll
-      for (int round = 0; round < 2; ++round) {
-        uint32_t sraw[16], draw[16];
-        tmem_ld16(s_t + round * 16, sraw);
-        tmem_ld16(s_t + kDbKeys + round * 16, draw);
+        for (int j = 0; j < 4; ++j) {
+          const int pair = round * 4 + j;
+          const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
+          const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
+          float lo, hi;
+          unpack2(fma2(s2, c2, fma2(Half2<T>::widen(bw[j]), log2e2, nl1)), lo, hi);
+          f32x2 p = pack2(ex2(lo), ex2(hi));
+          if (bits != 0xffffffffu) p = select2(p, bits, 2 * pair);
+          acc2[pair] = fma2(p, add2(d2, nd1), acc2[pair]);
+        }
+      };
+      uint32_t s_a[8], d_a[8], s_b[8], d_b[8];
+      DB_CLK(l0);
+      tmem_ld8(s_t, s_a);
+      tmem_ld8(s_t + kTile, d_a);
+      tmem_wait_ld();
+      DB_CLK(l1);
+      DB_ADD(1, l1 - l0);
+      tmem_ld8(s_t + 8, s_b);
+      tmem_ld8(s_t + kTile + 8, d_b);
+      work8(0, s_a, d_a);
+      tmem_wait_ld();
+      tmem_ld8(s_t + 16, s_a);
+      tmem_ld8(s_t + kTile + 16, d_a);
+      work8(1, s_b, d_b);
+      tmem_wait_ld();
+      tmem_ld8(s_t + 24, s_b);
+      tmem_ld8(s_t + kTile + 24, d_b);
+      work8(2, s_a, d_a);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(DbSmem::sd_free + buf));
+      work8(3, s_b, d_b);
+#else
+#pragma unroll
+      for (int round = 0; round < 4; ++round) {
+        uint32_t sraw[8], draw[8];
+        DB_CLK(l0);
+        tmem_ld8(s_t + round * 8, sraw);
+        tmem_ld8(s_t + kTile + round * 8, draw);
         tmem_wait_ld();
-        if (round == 1) {
+        DB_CLK(l1);
+        DB_ADD(1, l1 - l0);
+        if (round == 3) {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(DbSmem::sd_free + buf));
         }
 #pragma unroll
-        for (int i8 = 0; i8 < 2; ++i8) {
-          const int c8 = round * 2 + i8;
-          f32x2 p2[4], ds2[4];
-          score_grad8<T, true>(sraw + i8 * 8, draw + i8 * 8, bias_row + ((((wg & 1) * 4 + c8) ^ (t & 7)) << 4), c2, log2e2, nl2,
-                               nd2, p2, ds2);
-          if (bits != 0xffffffffu) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) ds2[i] = select2(ds2[i], bits, c8 * 8 + 2 * i);
+        for (int j = 0; j < 4; ++j) {
+          const int pair = round * 4 + j;
+          const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
+          const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
+          f32x2 p;
+          if (kDbPolyEvery > 0 && (pair % (kDbPolyEvery > 0 ? kDbPolyEvery : 1)) == kDbPolyEvery - 1) {
+            // exponent x = s c + bias log2e - lse log2e, as u = sat((x - low) / 128)
+            float b_lo, b_hi, s_lo, s_hi;
+            unpack2(bias2[pair], b_lo, b_hi);
+            unpack2(s2, s_lo, s_hi);
+            const float u_lo = fma_sat(s_lo, c_unit, fmaf(b_lo, kUnit, nl_unit));
+            const float u_hi = fma_sat(s_hi, c_unit, fmaf(b_hi, kUnit, nl_unit));
+            p = ex2_poly_unit(pack2(u_lo, u_hi));
+          } else {
+            float lo, hi;
+            unpack2(fma2(s2, c2, add2(bias2[pair], nl1)), lo, hi);
+            p = pack2(ex2(lo), ex2(hi));
           }
+          if (bits != 0xffffffffu) p = select2(p, bits, 2 * pair);
+          acc2[pair] = fma2(p, add2(d2, nd1), acc2[pair]);
+        }
+      }
+#endif
+      DB_CLK(c2);
+      DB_ADD(2, c2 - c1);
+      DB_ADD(3, 1);
+    }
+    if (ok && q_valid) {
+      if (P.num_parts == 1) {
+        T* dst = reinterpret_cast<T*>(P.dbias) + b * P.db_sb + h * P.db_sh + int64_t(q_index) * P.db_sq + int64_t(key_base) * P.db_sk;
+        if (P.db_sk == 1 && key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc2[c8 * 4 + i] = add2(acc2[c8 * 4 + i], ds2[i]);
+          for (int c = 0; c < 4; ++c)
+            reinterpret_cast<uint4*>(dst)[c] = make_uint4(pack16<T>(acc2[4 * c]), pack16<T>(acc2[4 * c + 1]),
+                                                          pack16<T>(acc2[4 * c + 2]), pack16<T>(acc2[4 * c + 3]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float lo, hi;
+            unpack2(acc2[i], lo, hi);
+            if (key_base + 2 * i < P.cols) dst[int64_t(2 * i) * P.db_sk] = T(lo);
+            if (key_base + 2 * i + 1 < P.cols) dst[int64_t(2 * i + 1) * P.db_sk] = T(hi);
+          }
+        }
+      } else {
+        float* dst = P.parts + (((int64_t(part) * P.batch + b) * P.heads + h) * P.cols + q_index) * P.cols + key_base;
+        if (key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float a, b2, c, d;
+            unpack2(acc2[2 * i], a, b2);
+            unpack2(acc2[2 * i + 1], c, d);
+            reinterpret_cast<float4*>(dst)[i] = make_float4(a, b2, c, d);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float lo, hi;
+            unpack2(acc2[i], lo, hi);
+            if (key_base + 2 * i < P.cols) dst[2 * i] = lo;
+            if (key_base + 2 * i + 1 < P.cols) dst[2 * i + 1] = hi;
+          }
         }
       }
     }
-    float acc[32];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-    if (ok && q_valid) {
-      float* dst = P.parts + (((int64_t(part) * P.batch + b) * P.heads + h) * P.cols + q_index) * P.cols + key_base;
-      if (key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (key_base + i < P.cols) dst[i] = acc[i];
-      }
-    }
   }
-  teardown(abort_flag, tmem_base, kDbMmaWarp, 4 * kDbKeys);
+  teardown(abort_flag, tmem_base, kDbMmaWarp, 512);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1678,11 +1677,25 @@ uint64_t align256(uint64_t v) { return (v + 255) & ~uint64_t(255); }
 
 int64_t padded_cols(const oops_ta_problem& p) { return (int64_t(p.cols) + 7) & ~int64_t(7); }
 
+// Row parts of the shared-bias kernel: one CTA per (part, batch, head, 128 x 128 tile) at one CTA per SM.  The
+// smallest part count whose CTAs fill whole waves of the 148 SMs to 90 % is taken (the best one if none does);
+// with a single part the kernel stores the final gradient and no partial planes exist.
 int bias_parts(const oops_ta_problem& p) {
-  const int64_t ctas = int64_t(p.batch) * p.heads * ceil_div(p.cols, kTile) * ceil_div(p.cols, kDbKeys);
-  int64_t parts = ceil_div(4 * 148 * kDbCtasPerSm, ctas);
-  parts = std::max<int64_t>(1, std::min<int64_t>(parts, std::min<int64_t>(16, p.rows)));
-  return (int)parts;
+  const int64_t tiles = ceil_div(p.cols, kTile);
+  const int64_t ctas = int64_t(p.batch) * p.heads * tiles * tiles;
+  const int limit = (int)std::min<int64_t>(16, p.rows);
+  int best = 1;
+  double best_fill = 0.0;
+  for (int parts = 1; parts <= limit; ++parts) {
+    const int64_t total = ctas * parts;
+    const double fill = double(total) / double(ceil_div(total, 148) * 148);
+    if (fill > best_fill + 1e-9) {
+      best = parts;
+      best_fill = fill;
+    }
+    if (fill >= 0.9) return parts;
+  }
+  return best;
 }
 
 // rows of more than 6 query tiles are split into groups of query tiles, one CTA each
@@ -1718,7 +1731,7 @@ Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
   l.pair_parts = at;  // f32 partial planes of dK, then of dV, one per group of query tiles
   if (fused && fused_groups(p) > 1) at += 2 * fused_plane_bytes(p);
   l.parts = at;
-  if (g.dbias && p.bias_groups == 1)
+  if (g.dbias && p.bias_groups == 1 && bias_parts(p) > 1)
     at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
   l.total = at;
   return l;
@@ -1916,11 +1929,17 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     DbParams P{};
     status = encode_pair(&P.map_q, p, p.q, kTile, "query");
     if (!status) status = encode_pair(&P.map_dout, p, dout, kTile, "upstream gradient");
-    if (!status) status = encode_pair(&P.map_k, p, p.k, kDbKeys, "key");
-    if (!status) status = encode_pair(&P.map_v, p, p.v, kDbKeys, "value");
+    if (!status) status = encode_pair(&P.map_k, p, p.k, kTile, "key");
+    if (!status) status = encode_pair(&P.map_v, p, p.v, kTile, "value");
     if (!status) status = encode_bias(&P.map_bias, p, p.bias, p.bias_sq, p.bias_sh, p.bias_sg, p.bias_sb, kTile, "bias");
     if (status) return status;
-    P.parts = reinterpret_cast<float*>(base + layout.parts);
+    P.num_parts = bias_parts(p);
+    P.parts = P.num_parts > 1 ? reinterpret_cast<float*>(base + layout.parts) : nullptr;
+    P.dbias = g.dbias;
+    P.db_sb = g.dbias_sb;
+    P.db_sh = g.dbias_sh;
+    P.db_sq = g.dbias_sq;
+    P.db_sk = g.dbias_sk;
     P.lse = lse;
     P.delta = delta;
     P.mask = p.mask;
@@ -1932,11 +1951,9 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.cols = p.cols;
     P.heads = p.heads;
     P.tiles = (int)ceil_div(p.cols, kTile);
-    P.k_tiles = (int)ceil_div(p.cols, kDbKeys);
-    P.num_parts = bias_parts(p);
     P.rows_per_part = (int)ceil_div(p.rows, P.num_parts);
     P.scale = p.scale;
-    const unsigned grid = (unsigned)(int64_t(P.num_parts) * p.batch * p.heads * P.tiles * P.k_tiles);
+    const unsigned grid = (unsigned)(int64_t(P.num_parts) * p.batch * p.heads * P.tiles * P.tiles);
     auto kernel = ta_bwd_dbias_kernel<T>;
     status = reserve_smem(kernel, kDbSmemBytes);
     if (status) return status;
@@ -1944,13 +1961,15 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     count_launch();
     status = check_launch("tcgen05 shared-bias gradient");
     if (status) return status;
-    const int64_t plane = int64_t(p.batch) * p.heads * p.cols * p.cols;
-    reduce_parts_kernel<T><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(P.parts, P.num_parts, g.dbias, g.dbias_sb,
-                                                                               g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch,
-                                                                               p.heads, p.cols);
-    count_launch();
-    status = check_launch("tcgen05 shared-bias reduce");
-    if (status) return status;
+    if (P.num_parts > 1) {
+      const int64_t plane = int64_t(p.batch) * p.heads * p.cols * p.cols;
+      reduce_parts_kernel<T><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(P.parts, P.num_parts, g.dbias, g.dbias_sb,
+                                                                                 g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch,
+                                                                                 p.heads, p.cols);
+      count_launch();
+      status = check_launch("tcgen05 shared-bias reduce");
+      if (status) return status;
+    }
   }
   return OOPS_TA_OK;
 }
@@ -1978,15 +1997,16 @@ int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oop
 
 int backward_device_status(int reset) { return read_tu_device_status(reset); }
 
-#ifdef TA_PROFILE_WAITS
-extern "C" int oops_ta_debug_bwd_clocks(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_bwd_clk, sizeof(unsigned long long) * 48) != cudaSuccess) return 1;
+#ifdef TA_PROFILE_DB
+extern "C" int oops_ta_debug_db_clocks(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_db_clk, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
   if (reset) {
-    unsigned long long zero[48] = {0};
-    cudaMemcpyToSymbol(g_bwd_clk, zero, sizeof(zero));
+    unsigned long long zero[16] = {0};
+    cudaMemcpyToSymbol(g_db_clk, zero, sizeof(zero));
   }
   return 0;
 }
 #endif
+
 
 }  // namespace oops_ta

@@ -14,14 +14,6 @@ namespace {
 
 using namespace ptx;
 
-#ifdef TA_PROFILE_WAITS
-// clocks spent waiting, summed over CTAs: 0 s_full, 1 bias_full, 2 v_full(wg0), 3 o_final, 4 mma:p_full, 5 mma:k_full,
-// 6 mma:v, 7 producer:k_empty, 8 producer:v_empty, 9 producer:bias_empty, 10 softmax loop clocks (thread 0), 11 CTA count
-__device__ unsigned long long g_wait_clk[32];
-#define TA_ADD(slot, value) atomicAdd(&g_wait_clk[slot], (unsigned long long)(value))
-#else
-#define TA_ADD(slot, value)
-#endif
 
 constexpr int kStages = 3;                       // K/V ring depth
 constexpr int kKeys = 64;                        // keys per step
@@ -31,6 +23,10 @@ constexpr int kBiasBytes = kTile * kKeys * 2;    // 16 KiB: one 128 x 64 bias ti
 constexpr int kFwdThreads = 320;                 // 2 softmax warpgroups + producer warp + MMA warp
 constexpr int kFwdTmemCols = 256;                // S 2x64 | P 2x32 | O 2x32; two CTAs share an SM
 constexpr int kMaxKeepWords = 512;               // keep-bit table: one bit per key column, cols <= 16384
+#ifndef TA_FWD_POLY_EVERY
+#define TA_FWD_POLY_EVERY 0
+#endif
+constexpr int kFwdPolyEvery = TA_FWD_POLY_EVERY;  // every n-th pair of a thread's logits takes the polynomial exp2 (0: none)
 
 struct FwdSmem {
   static constexpr int q = 0;                          // [2]
@@ -173,14 +169,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
     // ------------------------------------------------------------------ producer (one thread)
     if (lane == 0) {
       bool ok = true;
-      TA_WAIT_SLOT(wk); TA_WAIT_SLOT(wv); TA_WAIT_SLOT(wb);
       for (int w = 0; w < n_tiles; ++w) {
         mbar_expect_tx(bar(FwdSmem::q_full + w), kQBytes);
         tma_load_5d(smem_base + FwdSmem::q + w * kQBytes, &P.map_q, bar(FwdSmem::q_full + w), 0, h, q0 + w * kTile, r, b);
       }
       for (int j = 0; j < KS && ok; ++j) {
         const int st = j % kStages, round = j / kStages;
-        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::k_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wk));
+        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::k_empty + st), (round - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_expect_tx(bar(FwdSmem::k_full + st), kKvBytes);
         tma_load_5d(smem_base + FwdSmem::k + st * kKvBytes, &P.map_k, bar(FwdSmem::k_full + st), 0, h, j * kKeys, r, b);
@@ -188,19 +183,18 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
           const int buf = j & 1;
           for (int w = 0; w < n_tiles && ok; ++w) {
             const int slot = w * 2 + buf;
-            if (j >= 2) ok = mbar_wait(bar(FwdSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag TA_WAIT_ARG(wb));
+            if (j >= 2) ok = mbar_wait(bar(FwdSmem::bias_empty + slot), ((j >> 1) - 1) & 1, abort_flag);
             if (!ok) break;
             mbar_expect_tx(bar(FwdSmem::bias_full + slot), kBiasBytes);
             tma_load_5d(smem_base + FwdSmem::bias + slot * kBiasBytes, &P.map_bias, bar(FwdSmem::bias_full + slot),
                         j * kKeys, q0 + w * kTile, h, g, b);
           }
         }
-        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::v_empty + st), (round - 1) & 1, abort_flag TA_WAIT_ARG(wv));
+        if (j >= kStages) ok = mbar_wait(bar(FwdSmem::v_empty + st), (round - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_expect_tx(bar(FwdSmem::v_full + st), kKvBytes);
         tma_load_5d(smem_base + FwdSmem::v + st * kKvBytes, &P.map_v, bar(FwdSmem::v_full + st), 0, h, j * kKeys, r, b);
       }
-      TA_ADD(7, wk); TA_ADD(8, wv); TA_ADD(9, wb);
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
@@ -209,7 +203,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       constexpr uint32_t idesc_qk = instr_desc(fmt, 0, 0, kTile, kKeys);
       constexpr uint32_t idesc_pv = instr_desc(fmt, 0, 1, kTile, kHeadDim);
       bool ok = true;
-      TA_WAIT_SLOT(wp); TA_WAIT_SLOT(wk); TA_WAIT_SLOT(wv);
       for (int w = 0; w < n_tiles && ok; ++w) ok = mbar_wait(bar(FwdSmem::q_full + w), 0, abort_flag);
       // S[128 x 64] = Q[128 x 32] K[64 x 32]^T; both K-major, 64-byte swizzle: 8-row groups 512 bytes apart,
       // each 16-channel step advances 32 bytes inside the swizzle span.
@@ -223,7 +216,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         mma_commit(bar(FwdSmem::s_full + w));
         if (w == n_tiles - 1) mma_commit(bar(FwdSmem::k_empty + st));
       };
-      if (ok) ok = mbar_wait(bar(FwdSmem::k_full), 0, abort_flag TA_WAIT_ARG(wk));
+      if (ok) ok = mbar_wait(bar(FwdSmem::k_full), 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
         for (int w = 0; w < n_tiles; ++w) issue_qk(0, w);
@@ -232,9 +225,9 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         if (j + 1 < KS) {
           // next score tiles: issued as soon as a warpgroup has pulled S(j) into registers, so that S(j+1) is
           // ready when its softmax of step j ends (P has its own tensor-memory columns)
-          ok = mbar_wait(bar(FwdSmem::k_full + (j + 1) % kStages), ((j + 1) / kStages) & 1, abort_flag TA_WAIT_ARG(wk));
+          ok = mbar_wait(bar(FwdSmem::k_full + (j + 1) % kStages), ((j + 1) / kStages) & 1, abort_flag);
           for (int w = 0; w < n_tiles && ok; ++w) {
-            ok = mbar_wait(bar(FwdSmem::s_free + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+            ok = mbar_wait(bar(FwdSmem::s_free + w), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
             issue_qk(j + 1, w);
@@ -242,11 +235,11 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         }
         const int st = j % kStages;
         for (int w = 0; w < n_tiles && ok; ++w) {
-          ok = mbar_wait(bar(FwdSmem::p_full + w), j & 1, abort_flag TA_WAIT_ARG(wp));
+          ok = mbar_wait(bar(FwdSmem::p_full + w), j & 1, abort_flag);
           if (ok && w == 0) {
-            ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
+            ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag);
             // with a mask, warpgroup 0 signs off every value step after clearing the rows of dropped keys
-            if (ok && signoff) ok = mbar_wait(bar(FwdSmem::v_ready + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wv));
+            if (ok && signoff) ok = mbar_wait(bar(FwdSmem::v_ready + st), (j / kStages) & 1, abort_flag);
           }
           if (!ok) break;
           tc_fence_after_sync();
@@ -263,7 +256,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
           if (w == n_tiles - 1) mma_commit(bar(FwdSmem::v_empty + st));
         }
       }
-      TA_ADD(4, wp); TA_ADD(5, wk); TA_ADD(6, wv);
     }
   } else if ((warp >> 2) < n_tiles) {
     // ------------------------------------------------------------------ softmax warpgroups
@@ -278,10 +270,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
     const f32x2 log2e2 = pack2(kLog2e, kLog2e);
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    TA_WAIT_SLOT(ws); TA_WAIT_SLOT(wbias); TA_WAIT_SLOT(wvf); TA_WAIT_SLOT(wo);
-#ifdef TA_PROFILE_WAITS
-    const long long loop_start = clock64();
-#endif
 
     for (int j = 0; j < KS && ok; ++j) {
       uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
@@ -296,7 +284,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         // Every step is signed off (one barrier phase per step); only steps with dropped keys are touched.
         const int st = j % kStages;
         if (!all_kept) {
-          ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag TA_WAIT_ARG(wvf));
+          ok = mbar_wait(bar(FwdSmem::v_full + st), (j / kStages) & 1, abort_flag);
           if (!ok) break;
           if (t < kKeys && ((bits[t >> 5] >> (t & 31)) & 1u) == 0) {
             uint4* row = reinterpret_cast<uint4*>(smem_gen + FwdSmem::v + st * kKvBytes + t * 64);
@@ -307,12 +295,9 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         mbar_arrive_warp(bar(FwdSmem::v_ready + st));
       }
 
-      ok = mbar_wait(bar(FwdSmem::s_full + w), j & 1, abort_flag TA_WAIT_ARG(ws));
+      ok = mbar_wait(bar(FwdSmem::s_full + w), j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-#ifdef TA_PROFILE_WAITS
-      const long long c0 = clock64();
-#endif
       f32x2 x[kKeys / 2];
 #pragma unroll
       for (int c = 0; c < kKeys / 32; ++c) {
@@ -324,13 +309,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(FwdSmem::s_free + w));
-#ifdef TA_PROFILE_WAITS
-      const long long c1 = clock64();
-#endif
 
       if (HAS_BIAS) {
         const int slot = w * 2 + (j & 1);
-        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag TA_WAIT_ARG(wbias));
+        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
         if (!ok) break;
         const uint8_t* row = smem_gen + FwdSmem::bias + slot * kBiasBytes + t * 128;
         uint4 bv[8];
@@ -382,23 +364,43 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       const f32x2 shift2 = pack2(shift, shift);
       f32x2 totals[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
       uint32_t packed[kKeys / 2];
+      if (kFwdPolyEvery > 0 && all_kept) {
+        // every kFwdPolyEvery-th pair takes its 2^x from the FMA pipe; steps with dropped keys (-inf logits, whose
+        // probability must be exactly zero) keep the special-function unit for every element
+        const float shift_unit = fmaf(shift, 1.f / 128.f, float(-kExp2PolyLow) / 128.f);
 #pragma unroll
-      for (int i = 0; i < kKeys / 2; ++i) {
-        float lo, hi;
-        unpack2(fma2(x[i], log2e2, shift2), lo, hi);
-        const float p0 = ex2(lo), p1 = ex2(hi);
-        totals[i & 3] = add2(totals[i & 3], pack2(p0, p1));
-        packed[i] = Half2<T>::pack(p0, p1);
+        for (int i = 0; i < kKeys / 2; ++i) {
+          f32x2 p;
+          if ((i % (kFwdPolyEvery > 0 ? kFwdPolyEvery : 1)) == kFwdPolyEvery - 1) {
+            float x_lo, x_hi;
+            unpack2(x[i], x_lo, x_hi);
+            p = ex2_poly_unit(pack2(fma_sat(x_lo, kLog2e / 128.f, shift_unit), fma_sat(x_hi, kLog2e / 128.f, shift_unit)));
+          } else {
+            float lo, hi;
+            unpack2(fma2(x[i], log2e2, shift2), lo, hi);
+            p = pack2(ex2(lo), ex2(hi));
+          }
+          totals[i & 3] = add2(totals[i & 3], p);
+          float p0, p1;
+          unpack2(p, p0, p1);
+          packed[i] = Half2<T>::pack(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kKeys / 2; ++i) {
+          float lo, hi;
+          unpack2(fma2(x[i], log2e2, shift2), lo, hi);
+          const float p0 = ex2(lo), p1 = ex2(hi);
+          totals[i & 3] = add2(totals[i & 3], pack2(p0, p1));
+          packed[i] = Half2<T>::pack(p0, p1);
+        }
       }
       float t_lo, t_hi;
       unpack2(add2(add2(totals[0], totals[1]), add2(totals[2], totals[3])), t_lo, t_hi);
       l_run = l_run * alpha + (t_lo + t_hi);
-#ifdef TA_PROFILE_WAITS
-      const long long c2 = clock64();
-#endif
       if (j > 0) {
         // the previous P V product must have finished with O and with the P columns before either is touched
-        ok = mbar_wait(bar(FwdSmem::pv_done + w), (j - 1) & 1, abort_flag TA_WAIT_ARG(wo));
+        ok = mbar_wait(bar(FwdSmem::pv_done + w), (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
       }
@@ -414,18 +416,9 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(FwdSmem::p_full + w));
-#ifdef TA_PROFILE_WAITS
-      if (t == 0) { const int o = n_tiles == 1 ? 16 : 0; TA_ADD(o + 12, c1 - c0); TA_ADD(o + 13, c2 - c1); TA_ADD(o + 14, clock64() - c2); TA_ADD(o + 15, 1); }
-#endif
     }
 
-#ifdef TA_PROFILE_WAITS
-    if (t == 0) { TA_ADD(10, clock64() - loop_start); TA_ADD(11, 1); }
-#endif
-    if (ok) ok = mbar_wait(bar(FwdSmem::o_final + w), 0, abort_flag TA_WAIT_ARG(wo));
-#ifdef TA_PROFILE_WAITS
-    if (t == 0) { TA_ADD(0, ws); TA_ADD(1, wbias); TA_ADD(2, wvf); TA_ADD(3, wo); }
-#endif
+    if (ok) ok = mbar_wait(bar(FwdSmem::o_final + w), 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       uint32_t acc[32];
@@ -461,7 +454,40 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
   teardown(abort_flag, tmem_base, 9, kFwdTmemCols);
 }
 
+// Self-test of the bounded wait: one CTA allocates tensor memory and waits, with a one-millisecond limit, on a barrier
+// that nothing ever completes.  The wait gives up, the CTA tears down exactly like a compute kernel whose wait ran
+// out (abort flag, grace period, status word, tensor memory freed) and returns by itself.
+__global__ void __launch_bounds__(128, 1) wait_limit_selftest_kernel() {
+  __shared__ __align__(8) uint64_t barrier_word;
+  __shared__ uint32_t tmem_slot_word;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const int warp = threadIdx.x >> 5;
+  if (device_failed()) return;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(smem_u32(&barrier_word), 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot_word), 32);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot_word);
+  if (threadIdx.x == 32) mbar_wait(smem_u32(&barrier_word), 0, abort_flag, 1000000ull);
+  teardown(abort_flag, tmem_base, 0, 32);
+}
+
 }  // namespace
+
+int wait_limit_selftest(cudaStream_t stream) {
+  wait_limit_selftest_kernel<<<1, 128, 0, stream>>>();
+  count_launch();
+  return check_launch("bounded-wait self-test");
+}
 
 bool tensor_forward_applies(const oops_ta_problem& p) {
   if (p.dtype != OOPS_TA_BF16 && p.dtype != OOPS_TA_F16) return false;
@@ -516,12 +542,10 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
   const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.q_pairs);
 
   auto launch = [&](auto kernel) -> int {
-    static thread_local const void* configured = nullptr;
-    if (configured != reinterpret_cast<const void*>(kernel)) {
-      const int rc = reserve_smem(kernel, kFwdSmemBytes);
-      if (rc) return rc;
-      configured = reinterpret_cast<const void*>(kernel);
-    }
+    // the attribute belongs to the (kernel, device) pair: it is set on every launch so that a host thread that
+    // moves between devices never launches without it (the call costs well under a microsecond)
+    const int rc = reserve_smem(kernel, kFwdSmemBytes);
+    if (rc) return rc;
     kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(P);
     count_launch();
     return check_launch("tcgen05 forward");
@@ -533,15 +557,5 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
 
 int forward_device_status(int reset) { return read_tu_device_status(reset); }
 
-#ifdef TA_PROFILE_WAITS
-extern "C" int oops_ta_debug_wait_clocks(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_wait_clk, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
-  if (reset) {
-    unsigned long long zero[32] = {0};
-    cudaMemcpyToSymbol(g_wait_clk, zero, sizeof(zero));
-  }
-  return 0;
-}
-#endif
 
 }  // namespace oops_ta

@@ -34,7 +34,7 @@ EXPORTS = (
     "oops_ta_abi_version", "oops_ta_status_string", "oops_ta_last_error", "oops_ta_supported",
     "oops_ta_uses_tensor_path", "oops_ta_forward_workspace_bytes", "oops_ta_backward_workspace_bytes",
     "oops_ta_forward", "oops_ta_backward", "oops_ta_launch_count", "oops_ta_device_status",
-    "oops_ta_forward_static", "oops_ta_forward_static_capacity",
+    "oops_ta_forward_static", "oops_ta_forward_static_capacity", "oops_ta_selftest_wait_limit",
 )
 
 
@@ -100,6 +100,8 @@ def library() -> ctypes.CDLL:
     lib.oops_ta_forward_static.argtypes = [POINTER(Problem), POINTER(Pair), c_void_p, c_void_p]
     lib.oops_ta_forward_static_capacity.restype = c_uint64
     lib.oops_ta_launch_count.restype = c_uint64
+    lib.oops_ta_selftest_wait_limit.restype = c_int
+    lib.oops_ta_selftest_wait_limit.argtypes = [c_void_p]
     lib.oops_ta_device_status.restype = c_int
     lib.oops_ta_device_status.argtypes = [c_int]
     if lib.oops_ta_abi_version() != ABI_VERSION:

@@ -22,6 +22,24 @@ def cuda() -> torch.device:
     return torch.device("cuda")
 
 
+def pytest_sessionfinish(session, exitstatus):
+    import parity_bounds
+
+    parity_bounds.write_report()
+
+
+@pytest.fixture(autouse=True)
+def device_status_stays_clear(request):
+    """After every GPU test the library's device-side status word must still be zero: a bounded wait that gave up
+    leaves its outputs undefined and makes later tensor kernels return at once until the word is cleared."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None and torch.cuda.is_available():
+        from oops_b200.runtime import cabi
+
+        status = cabi.device_status(reset=True)
+        assert status == 0, f"a kernel of this test recorded device status {status} ({cabi.status_message(status)})"
+
+
 @pytest.fixture(scope="session", autouse=True)
 def built_library():
     """Build the C-ABI library once if it is stale (nvcc cross-compiles without a GPU)."""

@@ -560,41 +560,9 @@ def test_config2_forward_padding_mask(cuda):
     assert torch.count_nonzero(out[:, 350:]) == 0
 
 
-def test_config3_training_shape(cuda):
-    """BASELINE config 3: bf16 forward+backward, N=768.  out/dq/dk/dv are checked against the f32 oracle
-    on a seeded subset of rows (rows are independent); dbias, which sums all rows, is checked against the
-    layout-agnostic f32-accumulating kernels (themselves checked against the oracle at smaller sizes) and
-    through additivity over a split of the rows."""
-    n = 768
-    q, k, v, bias, mask, upstream = baseline_inputs(n, torch.bfloat16)
-    dev = [t.to(cuda) for t in (q, k, v, bias)]
-    leaves = [t.detach().requires_grad_(True) for t in dev]
-    out = triangle_attention(leaves[0], leaves[1], leaves[2], mask.to(cuda), leaves[3])
-    dq, dk, dv, db = torch.autograd.grad(out, leaves, upstream.to(cuda))
-    rows = torch.randperm(n, generator=torch.Generator().manual_seed(1))[:6].sort().values
-    want = oracle.forward_backward(q[:, rows], k[:, rows], v[:, rows], mask[:, rows], bias, upstream[:, rows])
-    assert_within(out[:, rows], want[0], 2e-2, "out")
-    for name, got, ref in (("dq", dq, want[1]), ("dk", dk, want[2]), ("dv", dv, want[3])):
-        assert_within(got[:, rows], ref, 2e-2 * max(1.0, float(ref.abs().max())), name)
-    with layout_agnostic_kernels():
-        leaves2 = [t.detach().requires_grad_(True) for t in dev]
-        out2 = triangle_attention(leaves2[0], leaves2[1], leaves2[2], mask.to(cuda), leaves2[3])
-        db2 = torch.autograd.grad(out2, leaves2[3], upstream.to(cuda))[0]
-    tolerance = 2e-2 * max(1.0, float(db2.float().abs().max()))
-    assert_within(db, db2, tolerance, "dbias vs f32-accumulating kernels")
-    # additivity: dbias over all rows equals the sum of dbias over two halves of the rows
-    halves = []
-    for sl in (slice(0, n // 2), slice(n // 2, n)):
-        part = [dev[i][:, sl].detach().requires_grad_(i < 0) for i in range(3)]
-        b = dev[3].detach().requires_grad_(True)
-        o = triangle_attention(part[0], part[1], part[2], mask.to(cuda)[:, sl], b)
-        halves.append(torch.autograd.grad(o, b, upstream.to(cuda)[:, sl])[0].float())
-    assert_within(db.float(), halves[0] + halves[1], tolerance, "dbias additivity")
-
-
 def test_config4_ending_node_ragged(cuda):
     """BASELINE config 4 at reduced lengths, where the oracle covers every row and every gradient (the full lengths
-    are covered by test_config4_full_lengths):
+    with token masks are covered by test_config_parity_gpu.py):
     ending-node ragged batch, bf16, forward+backward, shared bias, all-valid masks."""
     case = nested_case(torch.bfloat16, cuda, lengths=(160, 100), heads=4, dim=32, bias_kind="shared",
                        transposed=True, seed=4)
@@ -676,39 +644,6 @@ def test_config5_full_size_properties(cuda):
                   "dbias vs f32-accumulating kernels")
 
 
-def test_config4_full_lengths(cuda):
-    """BASELINE config 4 at its full lengths (ending-node ragged batch, lengths 1024 and 700, bf16, shared bias).
-    The packed call must agree bit for bit with one dense ending-node call per sample (same kernels, same tiles),
-    and a seeded sample of logical rows of each sample is checked against the f32 oracle."""
-    lengths, heads, dim = (1024, 700), 4, 32
-    gen = torch.Generator().manual_seed(6)
-    stored = {name: [(torch.randn(L, L, heads, dim, generator=gen) * 0.5).to(torch.bfloat16) for L in lengths] for name in "qkv"}
-    biases = [torch.randn(1, heads, L, L, generator=gen).to(torch.bfloat16) for L in lengths]
-    nested = {name: NestedTensor(stored[name], ragged_dims=(0, 1)) for name in "qkv"}
-    packed = {name: nested[name].packed_like(nested[name].concat.to(cuda)).transpose(-4, -3) for name in "qkv"}
-    bias_template = NestedTensor(biases, ragged_dims=(2, 3))
-    packed_bias = bias_template.packed_like(bias_template.concat.to(cuda)).transpose(-2, -1)
-    with torch.no_grad():
-        values = triangle_attention(packed["q"], packed["k"], packed["v"], None, packed_bias).concat
-    at = 0
-    for i, L in enumerate(lengths):
-        block = values[at : at + L * L].reshape(L, L, heads, dim)  # stored order of sample i
-        at += L * L
-        # the logical sample is the pair-axes transpose of the stored element (ending node)
-        logical = {name: stored[name][i].transpose(0, 1) for name in "qkv"}
-        logical_bias = biases[i].transpose(-2, -1)
-        with torch.no_grad():
-            dense = triangle_attention(
-                *(logical[name].to(cuda)[None] for name in "qkv"), None, logical_bias.to(cuda)[None]
-            )[0]
-        assert torch.equal(block.transpose(0, 1), dense), f"sample {i}: packed and dense calls differ"
-        rows = torch.randperm(L, generator=torch.Generator().manual_seed(7 + i))[:3].sort().values
-        want = oracle.forward(
-            logical["q"][None][:, rows], logical["k"][None][:, rows], logical["v"][None][:, rows], None, logical_bias[None]
-        )
-        assert_within(dense[None][:, rows], want, 2e-2, f"sample {i} out")
-
-
 def test_padded_dense_equals_ragged(cuda):
     """The padded dense form (token masks) and the packed ragged form agree on the valid region."""
     lengths, heads, dim, n = (48, 29), 2, 32, 48
@@ -736,16 +671,20 @@ def test_padded_dense_equals_ragged(cuda):
 # ------------------------------------------------------------------------------------------
 
 
-def test_c_abi_direct(cuda):
-    """Forward and reverse passes through the raw C entry points, no autograd in between."""
+@pytest.mark.parametrize("dtype,dim,cols", [(torch.float32, 24, 33), (torch.bfloat16, 32, 136)])
+def test_c_abi_direct(cuda, dtype, dim, cols):
+    """Forward and reverse passes through the raw C entry points, no autograd in between: once on the
+    layout-agnostic f32 kernels, once on the tcgen05 kernels (16-bit, head size 32)."""
     from oops_b200.runtime import cabi
 
     lib = cabi.library()
-    case = dense_case(torch.float32, dim=24, bias_kind="shared")
+    case = dense_case(dtype, dim=dim, cols=cols, bias_kind="shared", scale_inputs=1.0 if dtype is torch.float32 else 0.5)
     q, k, v, bias, up = (case[n].to(cuda) for n in ("q", "k", "v", "bias", "upstream"))
     mask = case["mask"].to(cuda)
-    problem = cabi.make_problem(q, k, v, mask, bias, 24**-0.5)
+    problem = cabi.make_problem(q, k, v, mask, bias, dim**-0.5)
     assert lib.oops_ta_supported(cabi.byref(problem)) == 0
+    assert lib.oops_ta_uses_tensor_path(cabi.byref(problem), 1) == (1 if dtype is torch.bfloat16 else 0)
+    atol = ATOL[dtype]
     scratch = torch.empty(int(lib.oops_ta_forward_workspace_bytes(cabi.byref(problem))) + 1, dtype=torch.uint8, device=cuda)
     problem.workspace, problem.workspace_bytes = scratch.data_ptr(), scratch.numel()
     out = torch.empty_like(q)
@@ -756,7 +695,7 @@ def test_c_abi_direct(cuda):
     assert lib.oops_ta_forward(cabi.byref(problem), cabi.byref(out_pair), lse.data_ptr(), stream) == 0
     assert cabi.launch_count() > before
     want = oracle_dense(case)
-    assert_within(out, want[0], 1e-4, "out")
+    assert_within(out, want[0], atol, "out")
     grads = cabi.Grads()
     dq, dk, dv, db = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(bias)
     grads.dq, grads.dk, grads.dv = cabi.pair_of(dq), cabi.pair_of(dk), cabi.pair_of(dv)
@@ -769,8 +708,38 @@ def test_c_abi_direct(cuda):
     assert lib.oops_ta_backward(cabi.byref(problem), cabi.byref(out_pair), cabi.byref(dout_pair), lse.data_ptr(),
                                 cabi.byref(grads), stream) == 0
     for name, got, ref in (("dq", dq, want[1]), ("dk", dk, want[2]), ("dv", dv, want[3]), ("dbias", db, want[4])):
-        assert_within(got, ref, 1e-4, name)
+        assert_within(got, ref, atol if dtype is torch.float32 else atol * max(1.0, float(ref.abs().max())), name)
     # a workspace that is too small is refused, not overrun
-    problem.workspace_bytes = 16
-    assert lib.oops_ta_forward(cabi.byref(problem), cabi.byref(out_pair), lse.data_ptr(), stream) == 6
+    if need > 16:
+        problem.workspace_bytes = 16
+        assert lib.oops_ta_backward(cabi.byref(problem), cabi.byref(out_pair), cabi.byref(dout_pair), lse.data_ptr(),
+                                    cabi.byref(grads), stream) == 6
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------------------
+# device-side status word
+# ------------------------------------------------------------------------------------------
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_cleared(cuda):
+    """A device-side wait that gives up is reported by the status word, stops later tensor kernels until the word is
+    cleared, and leaves the context usable.  The wait that runs out is the library's self-test kernel: one CTA waits
+    one millisecond on a barrier that nothing completes, then tears down like a compute kernel and returns."""
+    from oops_b200.attention.triangle.triangle_attention import checked_device_status
+    from oops_b200.runtime import cabi
+
+    lib = cabi.library()
+    assert cabi.device_status(reset=True) == 0
+    assert lib.oops_ta_selftest_wait_limit(torch.cuda.current_stream().cuda_stream) == 0
+    assert cabi.device_status(reset=False) == cabi.STATUS_DEVICE_TIMEOUT
+    case = dense_case(torch.bfloat16, dim=32, cols=72, bias_kind="shared", scale_inputs=0.5)
+    args, _ = to_device(case, cuda, active=())
+    # the word is still set: the forward tensor kernel returns at once, and a checked call says so (and clears it)
+    with checked_device_status(), torch.no_grad(), pytest.raises(RuntimeError, match="device status 8"):
+        triangle_attention(args["q"], args["k"], args["v"], args["mask"], args["bias"])
+    assert cabi.device_status(reset=False) == 0
+    # the next call is correct again
+    with checked_device_status(), torch.no_grad():
+        out = triangle_attention(args["q"], args["k"], args["v"], args["mask"], args["bias"])
+    assert_within(out, oracle_dense(case)[0], 2e-2, "out after the status word was cleared")

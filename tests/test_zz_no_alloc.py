@@ -5,9 +5,12 @@ memory pool is frozen after start-up, a latency-critical loop that cannot afford
 synchronisation of an allocation, or code that is recording work for later replay.  It keeps the logits of
 a block of pair rows in a fixed array inside the library instead of a caller-provided workspace.
 
-The test drives it through the C ABI twice in a row (the array keeps the previous call's contents) and
+The test drives it through the C ABI several times in a row (the array keeps the previous call's contents) and
 compares each result with `oops_ta_forward` on the same kernels (layout-agnostic path forced), which must
-agree bit for bit; it also checks that a problem whose single pair row does not fit is refused.
+agree bit for bit, and with the CPU oracle within the tolerance of the dtype.  One case has more pair rows than
+the array holds at once, so the entry point walks the rows in blocks that reuse the array within a single call
+(the regular call splits by its own, larger budget: equal bits also show that results do not depend on the block
+size).  A problem whose single pair row does not fit is refused.
 This file is named so that pytest collects it last.
 """
 
@@ -16,7 +19,10 @@ from __future__ import annotations
 import pytest
 import torch
 
+from oracle import triangle_oracle as oracle
+
 pytestmark = pytest.mark.gpu
+ATOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
 
 
 def _case(cuda, seed, rows, cols, heads, dim, dtype):
@@ -55,8 +61,10 @@ def test_static_forward_matches_regular_forward_twice(cuda):
     lib = cabi.library()
     stream = torch.cuda.current_stream().cuda_stream
     assert lib.oops_ta_forward_static_capacity() == 32 << 20
-    # two calls in a row with different shapes and dtypes: the second sees the first one's leftovers
-    for seed, rows, cols, heads, dim, dtype in ((0, 5, 70, 2, 24, torch.float32), (1, 9, 130, 4, 32, torch.bfloat16)):
+    # calls in a row with different shapes and dtypes: each sees the previous one's leftovers in the array.  The last
+    # case needs 4 MiB of logits per pair row (4 heads x 512^2 x 4 bytes), so its 16 rows take two blocks of 8.
+    cases = ((0, 5, 70, 2, 24, torch.float32), (1, 9, 130, 4, 32, torch.bfloat16), (2, 16, 512, 4, 16, torch.bfloat16))
+    for seed, rows, cols, heads, dim, dtype in cases:
         q, k, v, mask, bias = _case(cuda, seed, rows, cols, heads, dim, dtype)
         scale = dim**-0.5
         want_out, want_lse = _regular(lib, cabi, q, k, v, mask, bias, scale, stream)
@@ -64,6 +72,9 @@ def test_static_forward_matches_regular_forward_twice(cuda):
         torch.cuda.synchronize()
         assert torch.equal(got_out, want_out)
         assert torch.equal(got_lse, want_lse)
+        reference = oracle.forward(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), bias.cpu(), scale)
+        error = float((got_out.float().cpu() - reference).abs().max())
+        assert error <= ATOL[dtype], f"rows={rows} cols={cols} {dtype}: max-abs error {error:.3e} against the oracle"
 
 
 def test_static_forward_refuses_oversized_rows(cuda):
