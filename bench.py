@@ -1,6 +1,6 @@
 """Benchmark of the triangle-attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg3] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg3] [--impl ours|reference|reference-gpu]
 
 One "step" is one forward + backward call of starting-node triangle attention on
 synthetic inputs of the named BASELINE configuration (bf16, H=4, D=32, shared
@@ -9,9 +9,18 @@ pair rows are sharded across ranks; each step then also all-gathers the bias
 shards and reduce-scatters the bias gradient (strong scaling: the total work is
 fixed).  Rank 0 prints one JSON line.
 
+`value` is the device-resident rate; `e2e` is the same step through the public
+Python call with pinned host buffers: every input goes host -> device and every
+result (out, dq, dk, dv, dbias) device -> host inside the timed region, streamed
+in blocks of pair rows (rows are independent) so that the copies of neighbouring
+blocks run under a block's kernels.
+
 `--impl reference` times the reference's own CPU math (the oracle restatement of
 its PyTorch `_reference`) on the host cores, on a bounded sample of rows of the
-same configuration.
+same configuration.  `--impl reference-gpu` times the reference's own operator
+(its Triton kernels, from an offline install under baseline/_ref) on the same GPU
+when that install is present; it is a reported comparison, never part of the
+product path.
 """
 
 from __future__ import annotations
@@ -20,6 +29,7 @@ import argparse
 import json
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
@@ -37,6 +47,7 @@ WORKLOADS = {
     "cfg3": dict(n=768, heads=4, dim=32, label="config 3: starting node, bf16, fwd+bwd, B=1, N=768, H=4, D=32"),
 }
 FALLBACK_PEAK_TFLOPS = 1590.0
+METRIC = "triangle_attention_fwd_bwd_tflops"
 
 
 def flops(rows: int, cols: int, heads: int, dim: int, backward: bool) -> float:
@@ -118,6 +129,11 @@ def make_inputs(n, heads, dim, row_lo, row_hi, seed):
     return q, k, v, upstream, bias_shard, mask
 
 
+# ----------------------------------------------------------------------------------------------
+# reference arms
+# ----------------------------------------------------------------------------------------------
+
+
 class CpuOracle:
     """The oracle's forward+backward on a bounded sample of pair rows (rows are independent), timed on the host."""
 
@@ -176,7 +192,7 @@ def reference_arm(args, work):
     value = statistics.mean(rates)
     sample = f"{rows_used} of {n} rows per step (rows are independent), f32, all host threads"
     line = {
-        "impl": "reference", "metric": "triangle_attention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * statistics.mean(secs), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -187,25 +203,165 @@ def reference_arm(args, work):
     print(json.dumps(line), flush=True)
 
 
+def reference_gpu_arm(args, work):
+    """The reference's own operator (Triton kernels) on this GPU, from the offline install under baseline/_ref.
+
+    The install needs two modules that are not in this image: DanLing (only its container type is imported; dense
+    inputs never touch it) and the version file the reference's build generates; both are stood in for by empty
+    module objects.  Any failure prints an `unavailable` line and exits 0."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference-gpu", "unavailable": " ".join(str(why).split())[:300]}), flush=True)
+
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "oops").is_dir():
+        return unavailable("baseline/_ref holds no install of the reference")
+    if not torch.cuda.is_available():
+        return unavailable("no GPU")
+    try:
+        import types
+
+        sys.path.insert(0, str(ref_root))
+        danling, tensors = types.ModuleType("danling"), types.ModuleType("danling.tensors")
+        tensors.NestedTensor = type("NestedTensor", (), {})
+        danling.tensors = tensors
+        sys.modules.setdefault("danling", danling)
+        sys.modules.setdefault("danling.tensors", tensors)
+        version = types.ModuleType("oops._version")
+        version.__version__ = version.version = "0.0.0"
+        sys.modules.setdefault("oops._version", version)
+        import oops  # the reference package
+
+        n, heads, dim = work["n"], work["heads"], work["dim"]
+        device = torch.device("cuda", 0)
+        q, k, v, upstream, bias_shard, mask = (t.to(device) for t in make_inputs(n, heads, dim, 0, n, seed=100))
+        q, k, v, bias = (t.requires_grad_(True) for t in (q, k, v, bias_shard))
+
+        def step():
+            out = oops.triangle_attention(q, k, v, mask, bias)
+            return torch.autograd.grad(out, (q, k, v, bias), upstream)
+
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        with torch.no_grad():
+            for _ in range(3):
+                oops.triangle_attention(q, k, v, mask, bias)
+            start.record()
+            for _ in range(args.steps):
+                oops.triangle_attention(q, k, v, mask, bias)
+            stop.record()
+            torch.cuda.synchronize()
+            ms_fwd = start.elapsed_time(stop) / args.steps
+        value = flops(n, n, heads, dim, True) / (ms * 1e-3) / 1e12
+        line = {
+            "impl": "reference-gpu", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": work["label"], "kernels": "the reference's Triton kernels, stock tile tables"},
+            "fwd": {"ms": ms_fwd, "tflops": flops(n, n, heads, dim, False) / (ms_fwd * 1e-3) / 1e12},
+        }
+        print(json.dumps(line), flush=True)
+    except Exception as error:  # noqa: BLE001
+        unavailable(f"{type(error).__name__}: {error}")
+
+
+# ----------------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------------
+
+
+class StreamedStep:
+    """One training step through the public call with host buffers, streamed in blocks of pair rows.
+
+    Inputs live in pinned host memory; every block's q, k, v and upstream gradient are copied in on one stream, its
+    forward + backward run on the compute stream, and its out, dq, dk, dv are copied back on a third stream, so that
+    the copies of blocks i+1 and i-1 run under the kernels of block i.  The (sharded) bias goes in once per step; the
+    bias gradient is summed over the blocks in f32 on the device and comes back once.  One copy per tensor block."""
+
+    def __init__(self, host, device, run_block, blocks):
+        self.device, self.run_block = device, run_block
+        self.q, self.k, self.v, self.up, self.bias, self.mask = host
+        rows = self.q.shape[1]
+        self.blocks = [(i * rows // blocks, (i + 1) * rows // blocks) for i in range(blocks)]
+        self.out = [torch.empty_like(self.q).pin_memory() for _ in range(4)]  # out, dq, dk, dv
+        self.dbias = torch.empty_like(self.bias).pin_memory()
+        self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        block_rows = max(hi - lo for lo, hi in self.blocks)
+        shape = (1, block_rows, *self.q.shape[2:])
+        self.staging = [[torch.empty(shape, dtype=self.q.dtype, device=device) for _ in range(4)] for _ in range(2)]
+        self.mask_dev = self.mask.to(device)
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v, self.up, self.bias))
+        self.d2h_bytes = sum(t.numel() * t.element_size() for t in (*self.out, self.dbias))
+
+    def __call__(self):
+        main = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        with torch.cuda.stream(self.s_in):
+            bias = self.bias.to(self.device, non_blocking=True)
+        free = [None, None]  # per staging set: the event after which it may be overwritten
+        dbias_sum, keep = None, []
+        for index, (lo, hi) in enumerate(self.blocks):
+            stage = self.staging[index & 1]
+            with torch.cuda.stream(self.s_in):
+                if free[index & 1] is not None:
+                    self.s_in.wait_event(free[index & 1])
+                for dst, src in zip(stage, (self.q, self.k, self.v, self.up)):
+                    dst[:, : hi - lo].copy_(src[:, lo:hi], non_blocking=True)
+                arrived = self.s_in.record_event()
+            main.wait_event(arrived)
+            q, k, v, up = (t[:, : hi - lo] for t in stage)
+            results = self.run_block(q, k, v, bias, self.mask_dev[:, lo:hi], up)  # (out, dq, dk, dv, dbias)
+            dbias_sum = results[4].float() if dbias_sum is None else dbias_sum.add_(results[4])
+            done = main.record_event()
+            free[index & 1] = done
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                for dst, src in zip(self.out, results[:4]):
+                    dst[:, lo:hi].copy_(src, non_blocking=True)
+            keep.append(results)  # the blocks' results stay alive until the copies have been issued and waited for
+        final = dbias_sum.to(self.bias.dtype)
+        self.s_out.wait_stream(main)
+        with torch.cuda.stream(self.s_out):
+            self.dbias.copy_(final, non_blocking=True)
+        main.wait_stream(self.s_out)
+        main.wait_stream(self.s_in)
+        self._keep = (keep, final, bias)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg5")
-    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--impl", choices=("ours", "reference", "reference-gpu"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-extra", action="store_true", help="skip the secondary N=768 measurement")
+    parser.add_argument("--with-reference-gpu", action="store_true",
+                        help="also time the reference's own GPU operator (a child process) and report it beside ours")
     args = parser.parse_args()
     work = WORKLOADS[args.workload]
     if args.impl == "reference":
         reference_arm(args, work)
         return
+    if args.impl == "reference-gpu":
+        reference_gpu_arm(args, work)
+        return
 
     import torch.distributed as dist
 
     from oops_b200 import triangle_attention
-    from oops_b200.distributed.row_shard import row_sharded_triangle_attention, shard_bounds
+    from oops_b200.distributed.row_shard import gather_bias, row_sharded_triangle_attention, shard_bounds
     from oops_b200.runtime import cabi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -224,16 +380,13 @@ def main():
 
     n, heads, dim = work["n"], work["heads"], work["dim"]
     lo, hi = shard_bounds(n, world, rank)
-    host = [t.pin_memory() for t in make_inputs(n, heads, dim, lo, hi, seed=100 + rank)]
-    q, k, v, upstream, bias_shard, mask = (t.to(device) for t in host)
-    q, k, v, bias_shard = (t.requires_grad_(True) for t in (q, k, v, bias_shard))
 
     def step(q, k, v, bias_shard, mask, upstream):
         if distributed:
             out = row_sharded_triangle_attention(q, k, v, mask, bias_shard)
         else:
             out = triangle_attention(q, k, v, mask, bias_shard)
-        return torch.autograd.grad(out, (q, k, v, bias_shard), upstream)
+        return (out, *torch.autograd.grad(out, (q, k, v, bias_shard), upstream))
 
     def barrier():
         if distributed:
@@ -254,6 +407,37 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    # ---- N > 1: the sharded call against the unsharded one on a small problem, before anything is timed ------
+    parity = None
+    if distributed:
+        n0 = 256
+        full = [t.to(device) for t in make_inputs(n0, heads, dim, 0, n0, seed=5)]  # every rank builds the same problem
+        fq, fk, fv, fup, fbias, fmask = full
+        leaves = [t.detach().requires_grad_(True) for t in (fq, fk, fv, fbias)]
+        whole = triangle_attention(leaves[0], leaves[1], leaves[2], fmask, leaves[3])
+        whole_grads = torch.autograd.grad(whole, leaves, fup)
+        a, b = shard_bounds(n0, world, rank)
+        mine = [t[:, a:b].detach().requires_grad_(True) for t in (fq, fk, fv)]
+        shard = fbias[:, :, :, a:b].detach().requires_grad_(True)
+        part = row_sharded_triangle_attention(mine[0], mine[1], mine[2], fmask[:, a:b], shard)
+        part_grads = torch.autograd.grad(part, (*mine, shard), fup[:, a:b])
+        errors = [float((part.float() - whole[:, a:b].float()).abs().max())]
+        errors += [float((g.float() - w[:, a:b].float()).abs().max()) for g, w in zip(part_grads[:3], whole_grads[:3])]
+        errors.append(float((part_grads[3].float() - whole_grads[3][:, :, :, a:b].float()).abs().max()))
+        worst = torch.tensor(errors, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        bound = 2e-2 * max(1.0, float(whole_grads[3].float().abs().max()))
+        parity = {"problem": f"N={n0}, {world} row shards against the unsharded call (max-abs, max over ranks)",
+                  "out": worst[0].item(), "dq": worst[1].item(), "dk": worst[2].item(), "dv": worst[3].item(),
+                  "dbias_shard": worst[4].item(), "dbias_bound": bound}
+        if max(parity["out"], parity["dq"], parity["dk"], parity["dv"]) != 0.0 or parity["dbias_shard"] > bound:
+            raise SystemExit(f"row-sharded results differ from the unsharded call: {parity}")
+        del full, leaves, whole, whole_grads, mine, shard, part, part_grads
+
+    host = [t.pin_memory() for t in make_inputs(n, heads, dim, lo, hi, seed=100 + rank)]
+    q, k, v, upstream, bias_shard, mask = (t.to(device) for t in host)
+    q, k, v, bias_shard = (t.requires_grad_(True) for t in (q, k, v, bias_shard))
+
     # ---- device-resident throughput --------------------------------------------------------
     for _ in range(args.warmup):
         step(q, k, v, bias_shard, mask, upstream)
@@ -266,32 +450,25 @@ def main():
     total_flops = flops(n, n, heads, dim, True)
     value = total_flops / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end: pinned host inputs in, gradient of the bias out, every step -------------
-    host_out = torch.empty(bias_shard.shape, dtype=torch.bfloat16).pin_memory()
-    h2d_bytes = sum(t.numel() * t.element_size() for t in host)
-    d2h_bytes = host_out.numel() * host_out.element_size()
+    # ---- end to end: every input in from pinned host memory, every result out, every step ----
+    def run_block(bq, bk, bv, bbias, bmask, bup):
+        leaves = [t.detach().requires_grad_(True) for t in (bq, bk, bv, bbias)]
+        return step(leaves[0], leaves[1], leaves[2], leaves[3], bmask, bup)
 
-    def e2e_step():
-        dq, dk, dv, up, bs, m = (t.to(device, non_blocking=True) for t in host)
-        dq, dk, dv, bs = (t.requires_grad_(True) for t in (dq, dk, dv, bs))
-        grads = step(dq, dk, dv, bs, m, up)
-        host_out.copy_(grads[3], non_blocking=True)
-
+    streamed = StreamedStep(host, device, run_block, blocks=max(1, min(8, (hi - lo) // 64)))
     e2e_iters = max(2, min(args.steps, 5))
-    e2e_step()
-    ms_e2e = timed(e2e_step, e2e_iters)
+    streamed()
+    ms_e2e = timed(streamed, e2e_iters)
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+    e2e = {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": streamed.h2d_bytes * world,
+           "d2h_bytes_per_step": streamed.d2h_bytes * world, "row_blocks": len(streamed.blocks),
+           "results_copied_back": ["out", "dq", "dk", "dv", "dbias"]}
+    del streamed
 
-    # ---- dominant kernel: the forward kernel, one launch per call, timed alone ---------------
+    # ---- the tensor kernels one by one -----------------------------------------------------------------
     peak, peak_sustained, peak_kind = measured_peak()
     with torch.no_grad():
-        bias_full = None
-        if distributed:
-            from oops_b200.distributed.row_shard import gather_bias
-
-            bias_full = gather_bias(bias_shard.detach())
-        else:
-            bias_full = bias_shard.detach()
+        bias_full = gather_bias(bias_shard.detach()) if distributed else bias_shard.detach()
         fwd = lambda: triangle_attention(q.detach(), k.detach(), v.detach(), mask, bias_full)  # noqa: E731
         for _ in range(3):
             fwd()
@@ -300,7 +477,6 @@ def main():
         fwd_launches = (cabi.launch_count() - before) // args.steps
     fwd_flops_rank = flops(hi - lo, n, heads, dim, False)
     fwd_tflops = fwd_flops_rank / (ms_fwd * 1e-3) / 1e12
-    # ---- the reverse-pass tensor kernels, each reached by asking for its gradients only ------------
     # dQ, dK and dV together take the single-pass kernel (five products); the bias gradient its own (two).  A call
     # also launches the row-dot kernel (and, for rows split into groups, the two partial-plane adds), a few percent
     # of the group, so a group's rate slightly understates its tensor kernel.
@@ -345,7 +521,7 @@ def main():
     }
 
     line = {
-        "metric": "triangle_attention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
@@ -356,11 +532,12 @@ def main():
         "frac_of_bf16_peak": value / (peak * world), "frac_of_bf16_sustained": value / (peak_sustained * world),
         "fwd": {"ms": ms_fwd, "tflops_per_gpu": fwd_tflops, "frac_of_bf16_peak": fwd_tflops / peak},
         "clocks": clocks.summary(),
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d_bytes * world,
-                "d2h_bytes_per_step": d2h_bytes * world},
+        "e2e": e2e,
         "gpu_launches": int(launches.item()),
         "roofline": roofline,
     }
+    if parity is not None:
+        line["parity"] = parity
     probe = cabi.make_problem(q.detach(), k.detach(), v.detach(), mask, bias_full, dim**-0.5)
     line["config"]["tensor_path"] = {
         "forward": bool(cabi.library().oops_ta_uses_tensor_path(cabi.byref(probe), 0) == 1),
@@ -386,6 +563,11 @@ def main():
             "fwd_frac_of_bf16_peak": f3f / ms3f / 1e9 / peak,
         }
 
+    # a kernel that gave up a bounded wait leaves undefined results: none may have
+    status = cabi.device_status(reset=False)
+    if status != 0:
+        raise SystemExit(f"a kernel recorded device status {status}; the measurements above are void")
+
     # ---- CPU baseline: the oracle on the host cores, bounded sample, rank 0 at N=1 only ------
     if rank == 0 and not distributed and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -394,6 +576,16 @@ def main():
             "value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
             "sample": f"{rows_used} of {n} rows (rows are independent), f32, {seconds:.1f} s",
         }
+    # ---- optional: the reference's own operator on the same GPU, in a child process ----------
+    if rank == 0 and not distributed and args.with_reference_gpu:
+        child = subprocess.run(
+            [sys.executable, str(Path(__file__).resolve()), "--impl", "reference-gpu", "--workload", args.workload,
+             "--steps", str(max(3, min(args.steps, 10))), "--warmup", "3"], capture_output=True, text=True, timeout=900,
+        )
+        reported = [ln for ln in child.stdout.splitlines() if ln.startswith("{")]
+        line["reference_gpu"] = json.loads(reported[-1]) if reported else {"unavailable": child.stderr[-300:]}
+        if "value" in line["reference_gpu"]:
+            line["reference_gpu"]["ours_over_reference"] = value / line["reference_gpu"]["value"]
     if rank == 0:
         print(json.dumps(line), flush=True)
     if distributed:

@@ -64,14 +64,21 @@ typedef enum oops_ta_status {
 /* flags of oops_ta_problem.flags */
 #define OOPS_TA_FLAG_FORCE_GENERIC 1u /* take the layout-agnostic FFMA kernels even
                                          where the tcgen05 kernels apply (testing) */
-#define OOPS_TA_FLAG_ALLOW_TF32 2u    /* f32 inputs may use TF32-class products; the
-                                         default keeps full f32 products, which is what
-                                         the reference's "ieee"/3xTF32 mode promises
-                                         (oops/runtime/dispatch.py:260-328)           */
-
 #define OOPS_TA_FLAG_SPLIT_REVERSE 4u /* reverse pass: take the separate dQ and dK/dV
                                          kernels even where the single-pass kernel that
                                          produces all three applies (testing)           */
+
+#define OOPS_TA_FLAG_DBIAS_F32 8u     /* reverse pass: the gradient buffer of a row-shared bias (bias_groups == 1)
+                                         holds f32 values whatever the bias type.  For callers that add the
+                                         gradients of several calls -- the row shards of one problem on several
+                                         GPUs -- and round once.  No counterpart in the reference, which has no
+                                         multi-GPU path.                                                         */
+#define OOPS_TA_FLAG_REUSE_DELTA 16u  /* reverse pass: the workspace already holds delta = rowsum(O * dO) from an
+                                         earlier oops_ta_backward call on the same problem, output, upstream
+                                         gradient and workspace; it is not recomputed.  Lets a caller split one
+                                         reverse pass into two calls (bias gradient first, so that its exchange
+                                         overlaps the other gradients) without paying for delta twice.  Honoured by
+                                         the tcgen05 kernels; the layout-agnostic kernels recompute.            */
 
 typedef struct oops_ta_pair {
   void* ptr;

@@ -229,11 +229,29 @@ def run_forward(
     return out, lse
 
 
+def backward_scratch_bytes(query, key, value, mask, bias, scale, flags, need) -> int:
+    """Scratch bytes the reverse pass of one dense ``(B, R, C, H, D)`` problem needs for this gradient request."""
+    lib = cabi.library()
+    problem = cabi.make_problem(query, key, value, mask, bias, scale, flags)
+    grads = cabi.Grads()
+    marker = cabi.Pair(1, 0, 0, 0, 0)  # the size query looks at which pointers are set, not at what they point to
+    none = cabi.Pair(None, 0, 0, 0, 0)
+    grads.dq, grads.dk, grads.dv = (marker if need[0] else none, marker if need[1] else none, marker if need[2] else none)
+    if need[3] and bias is not None:
+        grads.dbias = 1
+    return int(lib.oops_ta_backward_workspace_bytes(cabi.byref(problem), cabi.byref(grads)))
+
+
 def run_backward(
     geometry, grad_out: Tensor, query: Tensor, key: Tensor, value: Tensor, mask: Optional[Tensor],
     bias: Optional[Tensor], out: Tensor, lse: Tensor, scale: float, flags: int, need: Sequence[bool],
+    *, scratch: Optional[Tensor] = None, dbias_dtype: Optional[torch.dtype] = None,
 ) -> Tuple[Optional[Tensor], Optional[Tensor], Optional[Tensor], Optional[Tensor]]:
-    """Launch the reverse pass of every view; returns ``(dq, dk, dv, dbias)``."""
+    """Launch the reverse pass of every view; returns ``(dq, dk, dv, dbias)``.
+
+    ``scratch`` lends a caller-owned byte buffer to the call (it must be large enough for every view; without it one
+    buffer per view is allocated).  ``dbias_dtype`` overrides the type of the bias gradient buffer: ``torch.float32``
+    together with ``cabi.FLAG_DBIAS_F32`` in ``flags`` returns the unrounded f32 sums of a row-shared bias."""
     lib = cabi.library()
     device = query.device
     need_q, need_k, need_v, need_b = need
@@ -248,7 +266,7 @@ def run_backward(
     dq = like(query) if need_q else None
     dk = like(key) if need_k else None
     dv = like(value) if need_v else None
-    dbias = torch.empty(bias.shape, dtype=bias.dtype, device=device) if need_b else None
+    dbias = torch.empty(bias.shape, dtype=dbias_dtype or bias.dtype, device=device) if need_b else None
 
     sizes = geometry.lse_sizes(query)
     lse_views = _split_lse(lse, sizes)
@@ -270,10 +288,11 @@ def run_backward(
             if db_views[i] is not None:
                 grads.dbias = db_views[i].data_ptr()
                 (grads.dbias_sb, grads.dbias_sg, grads.dbias_sh, grads.dbias_sq, grads.dbias_sk) = db_views[i].stride()
-            scratch = _workspace(lib.oops_ta_backward_workspace_bytes(cabi.byref(problem), cabi.byref(grads)), device)
-            if scratch is not None:
-                problem.workspace = scratch.data_ptr()
-                problem.workspace_bytes = scratch.numel()
+            nbytes = lib.oops_ta_backward_workspace_bytes(cabi.byref(problem), cabi.byref(grads))
+            buffer = scratch if scratch is not None and scratch.numel() >= nbytes else _workspace(nbytes, device)
+            if buffer is not None:
+                problem.workspace = buffer.data_ptr()
+                problem.workspace_bytes = buffer.numel()
             out_pair, dout_pair = cabi.pair_of(o_views[i]), cabi.pair_of(do_views[i])
             status = lib.oops_ta_backward(
                 cabi.byref(problem), cabi.byref(out_pair), cabi.byref(dout_pair), lse_views[i].data_ptr(),

@@ -584,7 +584,8 @@ int generic_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oo
   if (shared_bias_grad) {
     const int64_t total = int64_t(p.batch) * p.heads * plane;
     shared_bias_store_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(
-        shared_acc, g.dbias, p.bias_dtype, g.dbias_sb, g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch, p.heads, p.cols);
+        shared_acc, g.dbias, (p.flags & OOPS_TA_FLAG_DBIAS_F32) != 0 ? int(OOPS_TA_F32) : p.bias_dtype, g.dbias_sb,
+        g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch, p.heads, p.cols);
     count_launch();
     const int status = check_launch("generic shared-bias store");
     if (status) return status;

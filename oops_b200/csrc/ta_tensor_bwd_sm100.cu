@@ -20,6 +20,8 @@
 // warpgroups of 128 threads that own one tensor-memory lane (= one query or key) each.  The dQ and dK/dV
 // kernels keep 256 tensor-memory columns and under 113 KB of shared memory, so two CTAs share an SM: their
 // MMA threads run independently and one CTA's prologue and epilogue overlap the other's steps.
+#include <type_traits>
+
 #include "ta_tensor_common.cuh"
 
 namespace oops_ta {
@@ -873,16 +875,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
 // ---------------------------------------------------------------------------------------------
 // fused dQ / dK / dV kernel: one pass over the score tiles of a pair row
 // ---------------------------------------------------------------------------------------------
-// CTA = (batch, row, head, group of up to 6 query tiles).  For every key tile and every query tile of the group:
-// S = Q K^T and dP = dO V^T (128 x 128, tensor memory) -> the four warpgroups (a thread owns a query, a warpgroup
-// 32 of the 128 keys) compute P and dS once and write them, 16-bit, into two shared-memory images whose rows
-// are queries and whose 128-byte-swizzled columns are keys.  The tensor core reads those images three ways:
-// dV += P^T dO and dK += dS^T Q take them as MN-major A operands (M = keys), dQ += dS K as a K-major A operand
+// CTA = (batch, row, head).  The row's query tiles are taken in groups of up to 6; for every group, every key tile and
+// every query tile of the group: S = Q K^T and dP = dO V^T (128 x 128, tensor memory) -> the four warpgroups (a thread
+// owns a query, a warpgroup 32 of the 128 keys) compute P and dS once and write them, 16-bit, into two shared-memory
+// images whose rows are queries and whose 128-byte-swizzled columns are keys.  The tensor core reads those images three
+// ways: dV += P^T dO and dK += dS^T Q take them as MN-major A operands (M = keys), dQ += dS K as a K-major A operand
 // (M = queries).  dQ of the group's query tiles, dK and dV of the current key tile stay in tensor memory:
 // S 128 | dP 128 | dK 32 | dV 32 | dQ 6 x 32 = 512 columns.  One `ex2` per logit and five products, where the
 // separate dQ and dK/dV kernels spend two and seven.  The images cost shared-memory bandwidth (64 KB written and
-// 96 KB read per 128 x 128 step), which is what bounds this kernel.  Rows of more than 768 columns are split into
-// groups; every group leaves f32 partial planes of dK and dV that a last kernel adds in a fixed order.
+// 96 KB read per 128 x 128 step), which is what bounds this kernel.
+// Rows of more than 768 columns have several groups.  The CTA walks them in order and carries the f32 sums of dK and
+// dV of every key tile from group to group in a scratch slot that belongs to its SM (one CTA is resident per SM, so
+// the slot is private while the CTA runs, and at 128 bytes per key and tensor it stays in L2): the thread that owns a
+// key adds what the slot holds, and stores 16-bit dK/dV after the last group.  The order of the sums is fixed, so the
+// gradients are bitwise reproducible, and no partial planes or reduction kernels exist.
 
 constexpr int kFMaxQTiles = 6;
 constexpr int kFThreads = 608;  // 16 element-wise warps, TMA producer, score issuer, accumulation issuer
@@ -890,6 +896,7 @@ constexpr int kFProducerWarp = 16, kFScoreWarp = 17, kFAccWarp = 18;
 constexpr int kFImage = 2 * 16384;       // P or dS of a step: two 64-key halves of 128 rows x 128 bytes
 constexpr int kFBias = 2 * kBiasStep;    // 128 x 128 bias tile as two 64-key boxes (staging: copied to registers at once)
 constexpr int kFKeepWords = 128;         // keep-bit table of a row
+constexpr int kFSlots = 256;             // scratch slots of the group-to-group sums: one per SM id
 
 struct FSmem {
   static constexpr int q = 0;                          // [3] 128 x 32 (a slot is held until the step's dK product ends)
@@ -913,7 +920,8 @@ struct FSmem {
   static constexpr int pds_done = pds_full + 2;        // [2] the dK and dQ products have consumed the dS image
   static constexpr int p_done = pds_done + 2;          // the dV products have consumed the P image
   static constexpr int dkv_free = p_done + 1;          // dK and dV of a finished key tile have been read out
-  static constexpr int num_bars = dkv_free + 1;
+  static constexpr int dq_free = dkv_free + 1;         // dQ of a finished group of query tiles has been read out
+  static constexpr int num_bars = dq_free + 1;
   static constexpr int tmem_slot = bars + num_bars * 8;
   static constexpr int abort_flag = tmem_slot + 4;
   static constexpr int drop_flags = abort_flag + 4;    // [16]
@@ -926,8 +934,8 @@ static_assert(kFSmemBytes <= 232448, "fused reverse kernel: shared memory over t
 struct FParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
   oops_ta_pair dq, dk, dv;
-  float* dk_parts;  // [groups][batch][rows][cols][heads][32] f32, used when groups > 1
-  float* dv_parts;
+  float* slots;     // [kFSlots][2][slot_keys][32] f32: sums of dK and dV carried from group to group (groups > 1)
+  int64_t slot_keys;
   const float* lse;
   const float* delta;
   const uint8_t* mask;
@@ -936,6 +944,29 @@ struct FParams {
   int q_tiles, k_tiles, groups, tiles_per_group;
   int write_dq, write_dk, write_dv;
   float scale;
+};
+
+// The walk over a pair row's steps, identical in every role of the kernel: groups of query tiles outermost, then key
+// tiles, then the query tiles of the group.  Ring slots and barrier phases count steps and key tiles across groups.
+struct FWalk {
+  int tiles_per_group, q_tiles, k_tiles, groups;
+  int g, kt, qi, nq;  // group, key tile, query tile within the group, query tiles of the group
+  int s, ktc;         // steps and key tiles walked so far
+  __device__ FWalk(const FParams& P)
+      : tiles_per_group(P.tiles_per_group), q_tiles(P.q_tiles), k_tiles(P.k_tiles), groups(P.groups), g(0), kt(0), qi(0),
+        nq(min(P.tiles_per_group, P.q_tiles)), s(0), ktc(0) {}
+  __device__ bool done() const { return g >= groups; }
+  __device__ int qt() const { return g * tiles_per_group + qi; }
+  __device__ void next() {
+    ++s;
+    if (++qi < nq) return;
+    qi = 0;
+    ++ktc;
+    if (++kt < k_tiles) return;
+    kt = 0;
+    ++g;
+    nq = min(tiles_per_group, q_tiles - g * tiles_per_group);
+  }
 };
 
 template <typename T, bool HAS_BIAS>
@@ -951,17 +982,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
-  const int group = idx % P.groups;
-  idx /= P.groups;
   const int h = idx % P.heads;
   idx /= P.heads;
   const int r = idx % P.rows;
   const int b = idx / P.rows;
-  const int qt0 = group * P.tiles_per_group;
-  const int nq = min(P.tiles_per_group, P.q_tiles - qt0);
   const int KT = P.k_tiles;
-  const int steps = KT * nq;  // step s: key tile s / nq, query tile qt0 + s % nq
-  const int g = P.bias_groups == 1 ? 0 : r;
+  const int bias_group = P.bias_groups == 1 ? 0 : r;
   const bool has_mask = P.mask != nullptr;
   const bool has_bits = has_mask || (P.cols % kTile) != 0;
   // tensor-memory columns
@@ -988,6 +1014,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     mbar_init(bar(FSmem::sd_full), 1);
     mbar_init(bar(FSmem::sd_free), 16);
     mbar_init(bar(FSmem::dkv_free), 8);
+    mbar_init(bar(FSmem::dq_free), 16);
     fence_barrier_init();
   }
   if (warp == kFScoreWarp) {
@@ -1028,12 +1055,11 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   if (warp == kFProducerWarp) {
     if (lane == 0) {
       bool ok = true;
-      int kt = 0, qi = 0;
-      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-        const int qt = qt0 + qi, qs = s % 3;
-        if (qi == 0) {
-          const int ks = kt & 1;
-          if (kt >= 2) ok = mbar_wait(bar(FSmem::kv_empty + ks), ((kt >> 1) - 1) & 1, abort_flag);
+      for (FWalk w(P); !w.done() && ok; w.next()) {
+        const int s = w.s, kt = w.kt, qt = w.qt(), qs = s % 3;
+        if (w.qi == 0) {
+          const int ks = w.ktc & 1;
+          if (w.ktc >= 2) ok = mbar_wait(bar(FSmem::kv_empty + ks), ((w.ktc >> 1) - 1) & 1, abort_flag);
           if (!ok) break;
           mbar_expect_tx(bar(FSmem::kv_full + ks), 2 * kBigTile);
           tma_load_5d(smem_base + FSmem::k + ks * kBigTile, &P.map_k, bar(FSmem::kv_full + ks), 0, h, kt * kTile, r, b);
@@ -1050,7 +1076,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
           mbar_expect_tx(bar(FSmem::bias_full), kFBias);
           for (int box = 0; box < 2; ++box)
             tma_load_5d(smem_base + FSmem::bias + box * kBiasStep, &P.map_bias, bar(FSmem::bias_full), kt * kTile + box * 64,
-                        qt * kTile, h, g, b);
+                        qt * kTile, h, bias_group, b);
         }
       }
     }
@@ -1058,13 +1084,12 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
       bool ok = true;
-      int kt = 0, qi = 0;
-      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-        const int qs = s % 3, ks = kt & 1;
+      for (FWalk w(P); !w.done() && ok; w.next()) {
+        const int s = w.s, qs = s % 3, ks = w.ktc & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
-        if (ok && qi == 0) {
-          ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
-          if (ok && signoff) ok = mbar_wait(bar(FSmem::k_ready + ks), (kt >> 1) & 1, abort_flag);
+        if (ok && w.qi == 0) {
+          ok = mbar_wait(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
+          if (ok && signoff) ok = mbar_wait(bar(FSmem::k_ready + ks), (w.ktc >> 1) & 1, abort_flag);
         }
         if (ok && s > 0) ok = mbar_wait(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
         if (!ok) break;
@@ -1088,14 +1113,15 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       constexpr uint32_t idesc_t = instr_desc(fmt, 1, 1, kTile, kHeadDim);  // A = image^T (M = keys), B MN-major
       constexpr uint32_t idesc_q = instr_desc(fmt, 0, 1, kTile, kHeadDim);  // A = image (M = queries), B MN-major
       bool ok = true;
-      int kt = 0, qi = 0;
-      for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-        const int qs = s % 3, ks = kt & 1;
+      for (FWalk w(P); !w.done() && ok; w.next()) {
+        const int s = w.s, kt = w.kt, qi = w.qi, qs = s % 3, ks = w.ktc & 1;
         ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
-        if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
+        if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
         if (ok) ok = mbar_wait(bar(FSmem::pds_full + (s & 1)), (s >> 1) & 1, abort_flag);
-        // dK and dV of the previous key tile must have been read out before they are overwritten
-        if (ok && qi == 0 && kt > 0) ok = mbar_wait(bar(FSmem::dkv_free), (kt - 1) & 1, abort_flag);
+        // dK and dV of the previous key tile must have been read out before they are overwritten,
+        // and so must dQ of the previous group of query tiles
+        if (ok && qi == 0 && w.ktc > 0) ok = mbar_wait(bar(FSmem::dkv_free), (w.ktc - 1) & 1, abort_flag);
+        if (ok && qi == 0 && kt == 0 && w.g > 0) ok = mbar_wait(bar(FSmem::dq_free), (w.g - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss + (s & 1) * kFImage;
@@ -1117,7 +1143,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
                  kdesc + uint64_t(kk * (1024 >> 4)), idesc_q, (kt > 0 || kk > 0) ? 1u : 0u);
         mma_commit(bar(FSmem::pds_done + (s & 1)));
         mma_commit(bar(FSmem::qd_empty + qs));
-        if (qi == nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
+        if (qi == w.nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
       }
     }
   } else if (warp < 16) {
@@ -1128,18 +1154,22 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     const float scale = P.scale;
     const f32x2 c2 = pack2(scale * kLog2e, scale * kLog2e), log2e2 = pack2(kLog2e, kLog2e);
     const int64_t stat_base = ((int64_t(b) * P.rows + r) * P.heads + h) * P.cols;
-    // statistics of this thread's query in the step's query tile, fetched one step ahead and left untouched till then
-    auto fetch_stats = [&](int s, int qi_of_s, float& lse_raw, float& delta_raw) {
+    // statistics of this thread's query in a step's query tile, fetched one step ahead and left untouched till then
+    auto fetch_stats = [&](const FWalk& at, float& lse_raw, float& delta_raw) {
       lse_raw = INFINITY;
       delta_raw = 0.f;
-      const int q = (qt0 + qi_of_s) * kTile + t;
-      if (s < steps && q < P.cols) {
+      const int q = at.qt() * kTile + t;
+      if (!at.done() && q < P.cols) {
         lse_raw = ldg_f32_here(P.lse + stat_base + q);
         delta_raw = ldg_f32_here(P.delta + stat_base + q);
       }
     };
-    // dK (warpgroup 0) and dV (warpgroup 1) of key tile kt: lanes are keys
-    auto store_key_tile = [&](int kt) {
+    uint32_t sm_id;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_id));
+    // dK (warpgroup 0) and dV (warpgroup 1) of key tile kt, complete for the query tiles of group g: lanes are keys.
+    // With several groups the f32 sums travel from group to group through this SM's scratch slot (the same thread
+    // owns a key in every group), and the last group stores the 16-bit result.
+    auto store_key_tile = [&](int g, int kt) {
       if (wg > 1) return;
       uint32_t acc[32];
       tmem_ld32(lanes_t + (wg == 0 ? kDkCol : kDvCol), acc);
@@ -1151,30 +1181,67 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       const bool wanted = wg == 0 ? P.write_dk != 0 : P.write_dv != 0;
       if (!wanted) return;
       if (P.groups > 1) {
-        float* dst = (wg == 0 ? P.dk_parts : P.dv_parts) +
-                     ((((int64_t(group) * P.batch + b) * P.rows + r) * P.cols + key) * P.heads + h) * kHeadDim;
+        float4* slot = reinterpret_cast<float4*>(P.slots + ((int64_t(sm_id) * 2 + wg) * P.slot_keys + key) * kHeadDim);
+        if (g > 0) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
-                                                           __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
-      } else {
-        const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
-        T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
-        store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
+          for (int i = 0; i < 8; ++i) {
+            const float4 carried = slot[i];
+            acc[4 * i] = __float_as_uint(__uint_as_float(acc[4 * i]) + carried.x);
+            acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + carried.y);
+            acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + carried.z);
+            acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + carried.w);
+          }
+        }
+        if (g < P.groups - 1) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            slot[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]), __uint_as_float(acc[4 * i + 2]),
+                                  __uint_as_float(acc[4 * i + 3]));
+          return;
+        }
       }
+      const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
+      T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
+      store_row32<T>(dst, acc, wg == 0 ? scale : 1.f, pair_vec_ok(o));
     };
+    // dQ of the query tiles of group g (tile qi is read out by warpgroup qi % 4; lanes are queries); every warp then
+    // reports that the accumulators may be overwritten by the next group
+    auto store_query_tiles = [&](int g) {
+      const int tiles = min(P.tiles_per_group, P.q_tiles - g * P.tiles_per_group);
+      for (int qi = wg; qi < tiles; qi += 4) {
+        uint32_t acc[32];
+        tmem_ld32(lanes_t + kDqCol + qi * kHeadDim, acc);
+        tmem_wait_ld();
+        const int q_index = (g * P.tiles_per_group + qi) * kTile + t;
+        if (q_index < P.cols && P.write_dq) {
+          T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
+          store_row32<T>(dst, acc, scale, pair_vec_ok(P.dq));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive_warp(bar(FSmem::dq_free));
+    };
+    FWalk w(P);
     float lse_next, delta_next;
-    fetch_stats(0, 0, lse_next, delta_next);
+    fetch_stats(w, lse_next, delta_next);
     bool ok = true;
+    if (P.groups > 1 && sm_id >= uint32_t(kFSlots)) {  // no scratch slot for this SM id: give up like a wait that ran out
+      *abort_flag = 1;
+      ok = false;
+    }
 
     // bias row of this thread's query in the staging tile: box (wg >> 1), 16-byte chunks (wg & 1) * 4 .. + 3
     const uint8_t* bias_row = smem_gen + FSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
 
-    int kt = 0, qi = 0;
-    for (int s = 0; s < steps && ok; ++s, qi = qi + 1 == nq ? 0 : qi + 1, kt += qi == 0) {
-      const int buf = s & 1;
+    int last_g = 0, last_kt = 0;  // group and key tile of the previous step
+    for (; !w.done() && ok; last_g = w.g, last_kt = w.kt, w.next()) {
+      const int s = w.s, kt = w.kt, qi = w.qi, buf = s & 1;
       const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
-      fetch_stats(s + 1, qi + 1 == nq ? 0 : qi + 1, lse_next, delta_next);
+      {
+        FWalk ahead = w;
+        ahead.next();
+        fetch_stats(ahead, lse_next, delta_next);
+      }
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
       const uint32_t bits = has_bits ? keep_words[kt * 4 + wg] : 0xffffffffu;
       // The step's bias words go to registers at once and the staging tile is handed back, so that the next
@@ -1193,8 +1260,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       }
       if (signoff && qi == 0 && warp < 4) {
         // key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory
-        const int ks = kt & 1;
-        ok = mbar_wait(bar(FSmem::kv_full + ks), (kt >> 1) & 1, abort_flag);
+        const int ks = w.ktc & 1;
+        ok = mbar_wait(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
         if (!ok) break;
         if (((keep_words[kt * 4 + (t >> 5)] >> (t & 31)) & 1u) == 0) {
           uint4* row = reinterpret_cast<uint4*>(smem_gen + FSmem::k + ks * kBigTile + t * 64);
@@ -1251,65 +1318,28 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
             make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
       if (qi == 0 && s > 0) {
-        // a new key tile: dK and dV of the previous one are complete once the products of step s - 1 are
+        // a new key tile: dK and dV of the previous one are complete once the products of step s - 1 are (a commit
+        // covers every product issued before it); a new group also finds its predecessor's dQ complete
         ok = mbar_wait(bar(FSmem::pds_done + ((s - 1) & 1)), ((s - 1) >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        store_key_tile(kt - 1);
+        store_key_tile(last_g, last_kt);
+        if (kt == 0) store_query_tiles(last_g);
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(bar(FSmem::pds_full + buf));
     }
 
-    // every product has finished when the products of the last two steps have
-    if (ok && steps > 1) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 2) & 1)), ((steps - 2) >> 1) & 1, abort_flag);
-    if (ok) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 1) & 1)), ((steps - 1) >> 1) & 1, abort_flag);
-    if (ok) {
+    // every product has finished when the products of the last step have
+    const int steps = w.s;
+    if (ok && steps > 0) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 1) & 1)), ((steps - 1) >> 1) & 1, abort_flag);
+    if (ok && steps > 0) {
       tc_fence_after_sync();
-      store_key_tile(KT - 1);
-      // dQ of query tile qi is read out by warpgroup qi % 4 (lanes are queries)
-      for (int qi = wg; qi < nq; qi += 4) {
-        uint32_t acc[32];
-        tmem_ld32(lanes_t + kDqCol + qi * kHeadDim, acc);
-        tmem_wait_ld();
-        const int q_index = (qt0 + qi) * kTile + t;
-        if (q_index < P.cols && P.write_dq) {
-          T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
-          store_row32<T>(dst, acc, scale, pair_vec_ok(P.dq));
-        }
-      }
+      store_key_tile(P.groups - 1, KT - 1);
+      store_query_tiles(P.groups - 1);
     }
   }
   teardown(abort_flag, tmem_base, kFScoreWarp);
-}
-
-// Adds the f32 partial planes of dK or dV in a fixed order: one thread per (batch, row, column, head) vector of 32.
-template <typename T>
-__global__ void reduce_pair_parts_kernel(const float* parts, int groups, oops_ta_pair out, float scale, int batch, int rows,
-                                         int cols, int heads) {
-  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t vectors = int64_t(batch) * rows * cols * heads;
-  if (i >= vectors) return;
-  float total[32];
-#pragma unroll
-  for (int d = 0; d < 32; ++d) total[d] = 0.f;
-  for (int p = 0; p < groups; ++p) {
-    const float4* src = reinterpret_cast<const float4*>(parts + (int64_t(p) * vectors + i) * 32);
-#pragma unroll
-    for (int d = 0; d < 8; ++d) {
-      const float4 v = src[d];
-      total[4 * d] += v.x; total[4 * d + 1] += v.y; total[4 * d + 2] += v.z; total[4 * d + 3] += v.w;
-    }
-  }
-  const int h = i % heads;
-  const int c = (i / heads) % cols;
-  const int r = (i / (int64_t(heads) * cols)) % rows;
-  const int64_t b = i / (int64_t(heads) * cols * rows);
-  uint32_t acc[32];
-#pragma unroll
-  for (int d = 0; d < 32; ++d) acc[d] = __float_as_uint(total[d]);
-  T* dst = reinterpret_cast<T*>(out.ptr) + b * out.sb + int64_t(r) * out.sr + int64_t(c) * out.sc + h * out.sh;
-  store_row32<T>(dst, acc, scale, pair_vec_ok(out));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1332,9 +1362,6 @@ constexpr int kDbStage = 4 * kBigTile;  // Q | dO | K | V of one row: 128 x 32 e
 #ifndef TA_DB_POLY_EVERY
 #define TA_DB_POLY_EVERY 0
 #endif
-#ifndef TA_DB_VARIANT
-#define TA_DB_VARIANT 0
-#endif
 constexpr int kDbPolyEvery = TA_DB_POLY_EVERY;  // every n-th pair of a thread's logits takes the polynomial exp2 (0: none)
 struct DbSmem {
   static constexpr int bias = 0;                         // 128 queries x 128 keys as two 64-key boxes (prologue only)
@@ -1356,8 +1383,9 @@ static_assert(kDbSmemBytes <= 232448, "shared-bias kernel: shared memory over th
 struct DbParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
   float* parts;  // [parts][batch][heads][cols][cols] f32 (num_parts > 1)
-  void* dbias;   // final gradient in the bias type (num_parts == 1)
+  void* dbias;   // final gradient (num_parts == 1): the bias type, or f32 when dbias_f32 is set
   int64_t db_sb, db_sh, db_sq, db_sk;
+  int dbias_f32;
   const float* lse;
   const float* delta;
   const uint8_t* mask;
@@ -1367,14 +1395,6 @@ struct DbParams {
   float scale;
 };
 
-#ifdef TA_PROFILE_DB
-__device__ unsigned long long g_db_clk[16];
-#define DB_CLK(name) const long long name = clock64()
-#define DB_ADD(slot, v) do { if (lane == 0) atomicAdd(&g_db_clk[slot], (unsigned long long)(v)); } while (0)
-#else
-#define DB_CLK(name)
-#define DB_ADD(slot, v)
-#endif
 template <typename T>
 __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __grid_constant__ DbParams P) {
   extern __shared__ uint8_t smem_raw[];
@@ -1481,10 +1501,6 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
 
     // The thread's bias values, times log2(e), for the whole kernel.
     bool ok = mbar_wait(bar(DbSmem::bias_full), 0, abort_flag);
-#if TA_DB_VARIANT == 1
-    const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
-    const f32x2 log2e2 = pack2(kLog2e, kLog2e);
-#else
     f32x2 bias2[16];
     {
       const uint8_t* bias_row = smem_gen + DbSmem::bias + (wg >> 1) * kBiasStep + t * 128 + (((t & 7) ^ ((wg & 1) * 4)) << 4);
@@ -1499,7 +1515,6 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
         bias2[4 * c + 3] = mul2(Half2<T>::widen(v.w), log2e2);
       }
     }
-#endif
     f32x2 acc2[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc2[i] = pack2(0.f, 0.f);
@@ -1538,97 +1553,80 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       const uint32_t bits = need_bits ? __ballot_sync(0xffffffffu, keep_lane) : 0xffffffffu;
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
       const float nl_unit = fmaf(neg_lse2, kUnit, kUnitShift);
-      DB_CLK(c0);
       ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      DB_CLK(c1);
-      DB_ADD(0, c1 - c0);
       const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
-#if TA_DB_VARIANT == 1
-      // bias words from the staging tile (it stays resident); the tensor-memory loads of the next eight columns are
-      // in flight while the current eight are worked on
-      auto work8 = [&](int round, const uint32_t (&sraw)[8], const uint32_t (&draw)[8]) {
-        const uint4 bw4 = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, round));
-        const uint32_t bw[4] = {bw4.x, bw4.y, bw4.z, bw4.w};
+      // The row's 32 logits of this thread in four rounds of eight tensor-memory columns.  Rows with a dropped key
+      // take a second copy of the body that zeroes the dropped columns: a test per element inside one body would
+      // be compiled into selects that every row pays for.
+      auto row_body = [&](auto drops_keys) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int pair = round * 4 + j;
-          const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
-          const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
-          float lo, hi;
-          unpack2(fma2(s2, c2, fma2(Half2<T>::widen(bw[j]), log2e2, nl1)), lo, hi);
-          f32x2 p = pack2(ex2(lo), ex2(hi));
-          if (bits != 0xffffffffu) p = select2(p, bits, 2 * pair);
-          acc2[pair] = fma2(p, add2(d2, nd1), acc2[pair]);
+        for (int round = 0; round < 4; ++round) {
+          uint32_t sraw[8], draw[8];
+          tmem_ld8(s_t + round * 8, sraw);
+          tmem_ld8(s_t + kTile + round * 8, draw);
+          tmem_wait_ld();
+          if (round == 3) {
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(DbSmem::sd_free + buf));
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int pair = round * 4 + j;
+            const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
+            const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
+            f32x2 p;
+            if (kDbPolyEvery > 0 && (pair % (kDbPolyEvery > 0 ? kDbPolyEvery : 1)) == kDbPolyEvery - 1) {
+              // exponent x = s c + bias log2e - lse log2e, as u = sat((x - low) / 128)
+              float b_lo, b_hi, s_lo, s_hi;
+              unpack2(bias2[pair], b_lo, b_hi);
+              unpack2(s2, s_lo, s_hi);
+              const float u_lo = fma_sat(s_lo, c_unit, fmaf(b_lo, kUnit, nl_unit));
+              const float u_hi = fma_sat(s_hi, c_unit, fmaf(b_hi, kUnit, nl_unit));
+              p = ex2_poly_unit(pack2(u_lo, u_hi));
+            } else {
+              float lo, hi;
+              unpack2(fma2(s2, c2, add2(bias2[pair], nl1)), lo, hi);
+              p = pack2(ex2(lo), ex2(hi));
+            }
+            f32x2 dd = add2(d2, nd1);
+            if (decltype(drops_keys)::value) {
+              // a dropped key's row of K or V may hold anything, so its S and dP may be non-finite: both factors go to zero
+              p = select2(p, bits, 2 * pair);
+              dd = select2(dd, bits, 2 * pair);
+            }
+            acc2[pair] = fma2(p, dd, acc2[pair]);
+          }
         }
       };
-      uint32_t s_a[8], d_a[8], s_b[8], d_b[8];
-      DB_CLK(l0);
-      tmem_ld8(s_t, s_a);
-      tmem_ld8(s_t + kTile, d_a);
-      tmem_wait_ld();
-      DB_CLK(l1);
-      DB_ADD(1, l1 - l0);
-      tmem_ld8(s_t + 8, s_b);
-      tmem_ld8(s_t + kTile + 8, d_b);
-      work8(0, s_a, d_a);
-      tmem_wait_ld();
-      tmem_ld8(s_t + 16, s_a);
-      tmem_ld8(s_t + kTile + 16, d_a);
-      work8(1, s_b, d_b);
-      tmem_wait_ld();
-      tmem_ld8(s_t + 24, s_b);
-      tmem_ld8(s_t + kTile + 24, d_b);
-      work8(2, s_a, d_a);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive_warp(bar(DbSmem::sd_free + buf));
-      work8(3, s_b, d_b);
-#else
-#pragma unroll
-      for (int round = 0; round < 4; ++round) {
-        uint32_t sraw[8], draw[8];
-        DB_CLK(l0);
-        tmem_ld8(s_t + round * 8, sraw);
-        tmem_ld8(s_t + kTile + round * 8, draw);
-        tmem_wait_ld();
-        DB_CLK(l1);
-        DB_ADD(1, l1 - l0);
-        if (round == 3) {
-          tc_fence_before_sync();
-          mbar_arrive_warp(bar(DbSmem::sd_free + buf));
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int pair = round * 4 + j;
-          const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
-          const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
-          f32x2 p;
-          if (kDbPolyEvery > 0 && (pair % (kDbPolyEvery > 0 ? kDbPolyEvery : 1)) == kDbPolyEvery - 1) {
-            // exponent x = s c + bias log2e - lse log2e, as u = sat((x - low) / 128)
-            float b_lo, b_hi, s_lo, s_hi;
-            unpack2(bias2[pair], b_lo, b_hi);
-            unpack2(s2, s_lo, s_hi);
-            const float u_lo = fma_sat(s_lo, c_unit, fmaf(b_lo, kUnit, nl_unit));
-            const float u_hi = fma_sat(s_hi, c_unit, fmaf(b_hi, kUnit, nl_unit));
-            p = ex2_poly_unit(pack2(u_lo, u_hi));
-          } else {
-            float lo, hi;
-            unpack2(fma2(s2, c2, add2(bias2[pair], nl1)), lo, hi);
-            p = pack2(ex2(lo), ex2(hi));
-          }
-          if (bits != 0xffffffffu) p = select2(p, bits, 2 * pair);
-          acc2[pair] = fma2(p, add2(d2, nd1), acc2[pair]);
-        }
-      }
-#endif
-      DB_CLK(c2);
-      DB_ADD(2, c2 - c1);
-      DB_ADD(3, 1);
+      if (bits == 0xffffffffu)
+        row_body(std::false_type{});
+      else
+        row_body(std::true_type{});
     }
     if (ok && q_valid) {
-      if (P.num_parts == 1) {
+      if (P.num_parts == 1 && P.dbias_f32) {
+        float* dst = reinterpret_cast<float*>(P.dbias) + b * P.db_sb + h * P.db_sh + int64_t(q_index) * P.db_sq +
+                     int64_t(key_base) * P.db_sk;
+        if (P.db_sk == 1 && key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float a, b2, c, d;
+            unpack2(acc2[2 * i], a, b2);
+            unpack2(acc2[2 * i + 1], c, d);
+            reinterpret_cast<float4*>(dst)[i] = make_float4(a, b2, c, d);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float lo, hi;
+            unpack2(acc2[i], lo, hi);
+            if (key_base + 2 * i < P.cols) dst[int64_t(2 * i) * P.db_sk] = lo;
+            if (key_base + 2 * i + 1 < P.cols) dst[int64_t(2 * i + 1) * P.db_sk] = hi;
+          }
+        }
+      } else if (P.num_parts == 1) {
         T* dst = reinterpret_cast<T*>(P.dbias) + b * P.db_sb + h * P.db_sh + int64_t(q_index) * P.db_sq + int64_t(key_base) * P.db_sk;
         if (P.db_sk == 1 && key_base + 32 <= P.cols && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -1698,20 +1696,21 @@ int bias_parts(const oops_ta_problem& p) {
   return best;
 }
 
-// rows of more than 6 query tiles are split into groups of query tiles, one CTA each
+// rows of more than 6 query tiles are walked in groups of query tiles by one CTA
 int fused_groups(const oops_ta_problem& p) { return (int)ceil_div(ceil_div(p.cols, kTile), kFMaxQTiles); }
 
-uint64_t fused_plane_bytes(const oops_ta_problem& p) {
-  return align256(uint64_t(fused_groups(p)) * p.batch * p.rows * p.cols * p.heads * kHeadDim * sizeof(float));
+// scratch slots that carry the f32 sums of dK and dV from group to group: one per SM id, two tensors, 32 floats per key
+int64_t fused_slot_keys(const oops_ta_problem& p) { return ceil_div(p.cols, kTile) * kTile; }
+uint64_t fused_slot_bytes(const oops_ta_problem& p) {
+  return align256(uint64_t(kFSlots) * 2 * fused_slot_keys(p) * kHeadDim * sizeof(float));
 }
 
 // The single-pass kernel serves calls that want dQ together with dK or dV and no per-row bias gradient, on rows
-// whose keep-bit table fits its shared memory (4096 columns) and whose partial planes stay within 16 GiB of scratch.
+// whose keep-bit table fits its shared memory (4096 columns).
 bool fused_applies(const oops_ta_problem& p, const oops_ta_grads& g) {
   if ((p.flags & OOPS_TA_FLAG_SPLIT_REVERSE) != 0) return false;
   if (g.dbias && p.bias_groups > 1) return false;
   if (ceil_div(p.cols, 32) > kFKeepWords) return false;
-  if (fused_groups(p) > 1 && 2 * fused_plane_bytes(p) > (uint64_t(16) << 30)) return false;
   return g.dq.ptr != nullptr && (g.dk.ptr != nullptr || g.dv.ptr != nullptr);
 }
 
@@ -1728,8 +1727,8 @@ Layout workspace_layout(const oops_ta_problem& p, const oops_ta_grads& g) {
   const bool fused = fused_applies(p, g);
   if (p.bias_groups != 0 && (g.dk.ptr || g.dv.ptr) && !fused)
     at += align256(uint64_t(p.batch) * p.bias_groups * p.heads * p.cols * padded_cols(p) * 2);
-  l.pair_parts = at;  // f32 partial planes of dK, then of dV, one per group of query tiles
-  if (fused && fused_groups(p) > 1) at += 2 * fused_plane_bytes(p);
+  l.pair_parts = at;  // per-SM slots of the single-pass kernel (rows of more than one group of query tiles)
+  if (fused && fused_groups(p) > 1) at += fused_slot_bytes(p);
   l.parts = at;
   if (g.dbias && p.bias_groups == 1 && bias_parts(p) > 1)
     at += align256(uint64_t(bias_parts(p)) * p.batch * p.heads * p.cols * p.cols * sizeof(float));
@@ -1764,7 +1763,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
   const bool shared_bias_grad = g.dbias && p.bias_groups == 1;
   int status;
 
-  {  // delta = rowsum(O * dO)
+  if ((p.flags & OOPS_TA_FLAG_REUSE_DELTA) == 0) {  // delta = rowsum(O * dO)
     const int64_t total = int64_t(p.batch) * p.rows * p.heads * p.cols;
     const int vec_ok = (reinterpret_cast<uintptr_t>(out.ptr) & 15) == 0 && (reinterpret_cast<uintptr_t>(dout.ptr) & 15) == 0 &&
                        out.sb % 8 == 0 && out.sr % 8 == 0 && out.sc % 8 == 0 && out.sh % 8 == 0 && dout.sb % 8 == 0 &&
@@ -1808,10 +1807,10 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.tiles_per_group = (int)ceil_div(P.q_tiles, P.groups);
     P.scale = p.scale;
     if (P.groups > 1) {
-      P.dk_parts = reinterpret_cast<float*>(base + layout.pair_parts);
-      P.dv_parts = reinterpret_cast<float*>(base + layout.pair_parts + fused_plane_bytes(p));
+      P.slots = reinterpret_cast<float*>(base + layout.pair_parts);
+      P.slot_keys = fused_slot_keys(p);
     }
-    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads * P.groups);
+    const unsigned grid = (unsigned)(int64_t(p.batch) * p.rows * p.heads);
     auto go = [&](auto kernel) -> int {
       const int rc = reserve_smem(kernel, kFSmemBytes);
       if (rc) return rc;
@@ -1821,23 +1820,6 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     };
     status = has_bias ? go(ta_bwd_fused_kernel<T, true>) : go(ta_bwd_fused_kernel<T, false>);
     if (status) return status;
-    if (P.groups > 1) {
-      const int64_t vectors = int64_t(p.batch) * p.rows * p.cols * p.heads;
-      if (g.dk.ptr) {
-        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dk_parts, P.groups, g.dk, p.scale,
-                                                                                          p.batch, p.rows, p.cols, p.heads);
-        count_launch();
-        status = check_launch("tcgen05 dK reduce");
-        if (status) return status;
-      }
-      if (g.dv.ptr) {
-        reduce_pair_parts_kernel<T><<<(unsigned)ceil_div(vectors, 128), 128, 0, stream>>>(P.dv_parts, P.groups, g.dv, 1.f,
-                                                                                          p.batch, p.rows, p.cols, p.heads);
-        count_launch();
-        status = check_launch("tcgen05 dV reduce");
-        if (status) return status;
-      }
-    }
   }
 
   if (!fused && (g.dq.ptr || row_bias_grad)) {
@@ -1940,6 +1922,7 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     P.db_sh = g.dbias_sh;
     P.db_sq = g.dbias_sq;
     P.db_sk = g.dbias_sk;
+    P.dbias_f32 = (p.flags & OOPS_TA_FLAG_DBIAS_F32) != 0;
     P.lse = lse;
     P.delta = delta;
     P.mask = p.mask;
@@ -1963,9 +1946,12 @@ int run_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_t
     if (status) return status;
     if (P.num_parts > 1) {
       const int64_t plane = int64_t(p.batch) * p.heads * p.cols * p.cols;
-      reduce_parts_kernel<T><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(P.parts, P.num_parts, g.dbias, g.dbias_sb,
-                                                                                 g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch,
-                                                                                 p.heads, p.cols);
+      if (P.dbias_f32)
+        reduce_parts_kernel<float><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(
+            P.parts, P.num_parts, g.dbias, g.dbias_sb, g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch, p.heads, p.cols);
+      else
+        reduce_parts_kernel<T><<<(unsigned)ceil_div(plane, 256), 256, 0, stream>>>(
+            P.parts, P.num_parts, g.dbias, g.dbias_sb, g.dbias_sh, g.dbias_sq, g.dbias_sk, p.batch, p.heads, p.cols);
       count_launch();
       status = check_launch("tcgen05 shared-bias reduce");
       if (status) return status;
@@ -1996,17 +1982,5 @@ int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oop
 }
 
 int backward_device_status(int reset) { return read_tu_device_status(reset); }
-
-#ifdef TA_PROFILE_DB
-extern "C" int oops_ta_debug_db_clocks(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_db_clk, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
-  if (reset) {
-    unsigned long long zero[16] = {0};
-    cudaMemcpyToSymbol(g_db_clk, zero, sizeof(zero));
-  }
-  return 0;
-}
-#endif
-
 
 }  // namespace oops_ta

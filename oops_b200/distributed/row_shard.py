@@ -12,6 +12,15 @@ multi-GPU code; this module is new.
 Collectives go through ``torch.distributed`` (NCCL over NVLink/NVSwitch on GPUs,
 gloo in the CPU tests).  The attention kernels only ever read the gathered bias
 from the rank's own memory.
+
+On GPUs the exchange is laid out so that nothing is copied around it and nothing is rounded twice:
+
+* the shards are gathered head by head straight into the final ``(B, 1, H, C, C)`` buffer (within one head the ranks'
+  query rows are consecutive blocks of memory);
+* the reverse pass first runs the bias-gradient kernel alone, into an f32 buffer, and hands each head to a
+  reduce-scatter that sums the ranks' f32 partial sums; the collectives run on the communication stream while the
+  compute stream goes on with dQ, dK and dV (which reuse the row sums the first call left in the scratch buffer);
+  the summed shard is rounded to the bias type once, at the end.
 """
 
 from __future__ import annotations
@@ -33,37 +42,118 @@ def shard_bounds(rows: int, world_size: int, rank: int) -> Tuple[int, int]:
     return rank * per_rank, (rank + 1) * per_rank
 
 
+def _gather_into_place(shard: Tensor, group) -> Tensor:
+    """All-gather a ``(B, 1, H, C/P, C)`` shard along the query axis into a new ``(B, 1, H, C, C)`` tensor, one
+    collective per (batch, head): rank p's rows of a head are the p-th contiguous block of that head's plane."""
+    world = dist.get_world_size(group)
+    batch, groups, heads, own, cols = shard.shape
+    shard = shard.contiguous()
+    full = torch.empty((batch, groups, heads, world * own, cols), dtype=shard.dtype, device=shard.device)
+    for b in range(batch):
+        for g in range(groups):
+            for h in range(heads):
+                dist.all_gather_into_tensor(full[b, g, h].view(-1), shard[b, g, h].view(-1), group=group)
+    return full
+
+
+def _scatter_sum(full: Tensor, group, async_op: bool):
+    """Reduce-scatter a ``(B, 1, H, C, C)`` tensor along the query axis, one collective per (batch, head); returns the
+    ``(B, 1, H, C/P, C)`` sum shard and the pending work handles (empty unless ``async_op``)."""
+    world = dist.get_world_size(group)
+    batch, groups, heads, rows, cols = full.shape
+    shard = torch.empty((batch, groups, heads, rows // world, cols), dtype=full.dtype, device=full.device)
+    pending = []
+    if dist.get_backend(group) == "gloo":  # gloo has no reduce_scatter_tensor
+        summed = full.clone()
+        dist.all_reduce(summed, group=group)
+        rank = dist.get_rank(group)
+        shard.copy_(summed[:, :, :, rank * (rows // world) : (rank + 1) * (rows // world)])
+        return shard, pending
+    for b in range(batch):
+        for g in range(groups):
+            for h in range(heads):
+                work = dist.reduce_scatter_tensor(shard[b, g, h].view(-1), full[b, g, h].view(-1), group=group, async_op=async_op)
+                if async_op:
+                    pending.append(work)
+    return shard, pending
+
+
 class _GatherQueryAxis(torch.autograd.Function):
-    """all-gather along the query axis (dim -2); reverse pass: reduce-scatter of the gradient."""
+    """all-gather along the query axis (dim -2); reverse pass: reduce-scatter of the gradient.  Composable with any
+    local operator (the CPU tests pair it with a PyTorch restatement); gradients are exchanged in the bias type."""
 
     @staticmethod
     def forward(ctx, shard: Tensor, group) -> Tensor:
-        world = dist.get_world_size(group)
-        ctx.group, ctx.world = group, world
-        shard = shard.contiguous()
-        flat = torch.empty(world * shard.numel(), dtype=shard.dtype, device=shard.device)
-        dist.all_gather_into_tensor(flat, shard.view(-1), group=group)
-        stacked = flat.view(world, *shard.shape)
-        # (P, B, 1, H, C/P, C) -> (B, 1, H, P * C/P, C)
-        return stacked.permute(1, 2, 3, 0, 4, 5).reshape(*shard.shape[:3], world * shard.shape[3], shard.shape[4])
+        ctx.group = group
+        return _gather_into_place(shard, group)
 
     @staticmethod
     def backward(ctx, grad_full: Tensor):
-        world, group = ctx.world, ctx.group
-        b, g, h, c, k = grad_full.shape
-        stacked = grad_full.reshape(b, g, h, world, c // world, k).permute(3, 0, 1, 2, 4, 5).contiguous()
-        shard = torch.empty(stacked.shape[1:], dtype=grad_full.dtype, device=grad_full.device)
-        if dist.get_backend(group) == "gloo":  # gloo has no reduce_scatter_tensor
-            dist.all_reduce(stacked, group=group)
-            shard.copy_(stacked[dist.get_rank(group)])
-        else:
-            dist.reduce_scatter_tensor(shard.view(-1), stacked.view(-1), group=group)
+        shard, _ = _scatter_sum(grad_full.contiguous(), ctx.group, async_op=False)
         return shard, None
 
 
 def gather_bias(bias_shard: Tensor, group=None) -> Tensor:
     """Differentiable all-gather of a ``(B, 1, H, C/P, C)`` bias shard into ``(B, 1, H, C, C)``."""
     return _GatherQueryAxis.apply(bias_shard, group)
+
+
+class _RowShardedAttention(torch.autograd.Function):
+    """Local attention over this rank's rows with the bias exchange folded in (CUDA, one dense problem)."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, mask, bias_shard, scale, group, flags):
+        from ..attention.triangle import function as fn
+
+        bias = _gather_into_place(bias_shard, group)
+        needs_grad = any(ctx.needs_input_grad[i] for i in (0, 1, 2, 4))
+        out, lse = fn.run_forward(fn.DenseGeometry(), query, key, value, mask, bias, scale, flags, want_lse=needs_grad)
+        ctx.set_materialize_grads(False)
+        if needs_grad:
+            ctx.save_for_backward(query, key, value, mask, bias, out, lse)
+            ctx.scale, ctx.group, ctx.flags = scale, group, flags
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from ..attention.triangle import function as fn
+        from ..runtime import cabi
+
+        if grad_out is None:
+            return (None,) * 8
+        query, key, value, mask, bias, out, lse = ctx.saved_tensors
+        geometry = fn.DenseGeometry()
+        query, key, value, out = (geometry.canonical_pair(t) for t in (query, key, value, out))
+        grad_out = geometry.canonical_pair(grad_out.resolve_neg().to(query.dtype))
+        need_q, need_k, need_v, need_b = (ctx.needs_input_grad[i] for i in (0, 1, 2, 4))
+        device = query.device
+        # One scratch buffer serves both calls, so that the second finds the row sums of the first.
+        sizes = []
+        if need_b:
+            sizes.append(fn.backward_scratch_bytes(query, key, value, mask, bias, ctx.scale, ctx.flags | cabi.FLAG_DBIAS_F32,
+                                                   (False, False, False, True)))
+        if need_q or need_k or need_v:
+            sizes.append(fn.backward_scratch_bytes(query, key, value, mask, bias, ctx.scale, ctx.flags,
+                                                   (need_q, need_k, need_v, False)))
+        scratch = torch.empty(max(sizes + [1]), dtype=torch.uint8, device=device)
+        shard32, pending, reuse = None, [], 0
+        if need_b:
+            _, _, _, dbias32 = fn.run_backward(
+                geometry, grad_out, query, key, value, mask, bias, out, lse, ctx.scale, ctx.flags | cabi.FLAG_DBIAS_F32,
+                (False, False, False, True), scratch=scratch, dbias_dtype=torch.float32,
+            )
+            shard32, pending = _scatter_sum(dbias32, ctx.group, async_op=True)
+            reuse = cabi.FLAG_REUSE_DELTA
+        dq = dk = dv = None
+        if need_q or need_k or need_v:
+            dq, dk, dv, _ = fn.run_backward(
+                geometry, grad_out, query, key, value, mask, bias, out, lse, ctx.scale, ctx.flags | reuse,
+                (need_q, need_k, need_v, False), scratch=scratch,
+            )
+        for work in pending:
+            work.wait()  # the compute stream waits for the collective; the host does not
+        dbias_shard = None if shard32 is None else shard32.to(bias.dtype)
+        return dq, dk, dv, None, dbias_shard, None, None, None
 
 
 def row_sharded_triangle_attention(
@@ -89,8 +179,34 @@ def row_sharded_triangle_attention(
     Returns this rank's rows of the output.  In the reverse pass ``bias_shard.grad`` receives the
     bias gradient summed over the rows of *all* ranks for this rank's query rows.
     """
-    bias = None if bias_shard is None else gather_bias(bias_shard, group)
-    return attention(query, key, value, mask, bias, scale=scale)
+    fused_exchange = (
+        attention is triangle_attention and bias_shard is not None and query.is_cuda and query.dim() == 5
+        and query.dtype in (torch.float16, torch.bfloat16) and bias_shard.dtype == query.dtype and bias_shard.dim() == 5
+        and bias_shard.shape[1] == 1 and not torch.compiler.is_compiling()
+    )
+    if not fused_exchange:
+        bias = None if bias_shard is None else gather_bias(bias_shard, group)
+        return attention(query, key, value, mask, bias, scale=scale)
+    from ..attention.triangle.triangle_attention import (
+        _check_admission, _check_dense_shapes, _flags, _require_bool_mask, _unit_inner,
+    )
+
+    world = dist.get_world_size(group)
+    batch, rows, cols, heads, head_size = query.shape
+    if tuple(bias_shard.shape) != (batch, 1, heads, cols // world, cols) or cols % world != 0:
+        raise ValueError(
+            f"row_sharded_triangle_attention bias_shard shape {tuple(bias_shard.shape)} must be "
+            f"{(batch, 1, heads, 'cols/ranks', cols)} with cols divisible by the {world} ranks"
+        )
+    _check_dense_shapes(query, key, value, mask, None)
+    _require_bool_mask(mask)
+    _check_admission(query, key, value, mask, bias_shard, "requires CUDA float16/bfloat16 q/k/v of one dtype and shape")
+    q5 = _unit_inner(query)
+    k5 = q5 if key is query else _unit_inner(key)
+    v5 = q5 if value is query else k5 if value is key else _unit_inner(value)
+    mask3 = None if mask is None else mask.expand(batch, rows, cols)
+    scale = head_size**-0.5 if scale is None else float(scale)
+    return _RowShardedAttention.apply(q5, k5, v5, mask3, bias_shard, scale, group, _flags())
 
 
 __all__ = ["shard_bounds", "gather_bias", "row_sharded_triangle_attention"]

@@ -18,7 +18,8 @@ ABI_VERSION = 1
 F32, F16, BF16 = 0, 1, 2
 FLAG_FORCE_GENERIC = 1
 FLAG_SPLIT_REVERSE = 4
-FLAG_ALLOW_TF32 = 2
+FLAG_DBIAS_F32 = 8
+FLAG_REUSE_DELTA = 16
 
 STATUS_OK = 0
 STATUS_INVALID_ARGUMENT = 1
@@ -165,5 +166,6 @@ def launch_count() -> int:
 
 __all__ = [
     "ABI_VERSION", "EXPORTS", "LIB_PATH", "Pair", "Problem", "Grads", "library", "status_message", "pair_of",
-    "make_problem", "launch_count", "device_status", "byref", "FLAG_FORCE_GENERIC", "FLAG_ALLOW_TF32", "DTYPE_CODE",
+    "make_problem", "launch_count", "device_status", "byref", "FLAG_FORCE_GENERIC", "FLAG_SPLIT_REVERSE", "FLAG_DBIAS_F32",
+    "FLAG_REUSE_DELTA", "DTYPE_CODE",
 ]
