@@ -392,15 +392,27 @@ def _backward_op(
     out: Tensor, lse: Tensor, scale: float, geometry: List[int], flags: int, need: List[bool],
 ) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     geom = decode_geometry(geometry)
+    query_given, key_given, value_given, bias_given = query, key, value, bias
     query, key, value, out = (geom.canonical_pair(t) for t in (query, key, value, out))
     grad_out = geom.canonical_pair(grad_out.resolve_neg().to(query.dtype))
     if bias is not None:
         bias = geom.canonical_bias(bias)
     if mask is not None and not isinstance(geom, DenseGeometry):
         mask = mask.contiguous()
+    given = (query_given, key_given, value_given, bias_given)
     grads = run_backward(geom, grad_out, query, key, value, mask, bias, out, lse.contiguous(), scale, flags, need)
     empty = torch.empty(0, dtype=query.dtype, device=query.device)
-    return tuple(empty if g is None else g for g in grads)
+
+    def laid_out_like(grad, operand):
+        # the fake implementation promises the operand's own strides; a gradient computed on a re-laid copy
+        # (unaligned or non-unit-stride operands) is copied into that layout
+        if grad is None:
+            return empty
+        if operand is None or grad.stride() == operand.stride():
+            return grad
+        return torch.empty_like(operand).copy_(grad)
+
+    return tuple(laid_out_like(g, operand) for g, operand in zip(grads, given))
 
 
 @_backward_op.register_fake
