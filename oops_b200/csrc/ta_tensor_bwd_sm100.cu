@@ -1317,17 +1317,19 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
             make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
+      fence_proxy_async_smem();
+      mbar_arrive_warp(bar(FSmem::pds_full + buf));
       if (qi == 0 && s > 0) {
-        // a new key tile: dK and dV of the previous one are complete once the products of step s - 1 are (a commit
-        // covers every product issued before it); a new group also finds its predecessor's dQ complete
+        // A new key tile: dK and dV of the previous one are complete once the products of step s - 1 are (a commit
+        // covers every product issued before it); a new group also finds its predecessor's dQ complete.  The images of
+        // step s have been handed over above, so the read-out and its trips to global memory run under this step's
+        // products, which wait for the accumulators through dkv_free / dq_free only.
         ok = mbar_wait(bar(FSmem::pds_done + ((s - 1) & 1)), ((s - 1) >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         store_key_tile(last_g, last_kt);
         if (kt == 0) store_query_tiles(last_g);
       }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(bar(FSmem::pds_full + buf));
     }
 
     // every product has finished when the products of the last step have
