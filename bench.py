@@ -421,7 +421,7 @@ def main():
         shard = fbias[:, :, :, a:b].detach().requires_grad_(True)
         part = row_sharded_triangle_attention(mine[0], mine[1], mine[2], fmask[:, a:b], shard)
         part_grads = torch.autograd.grad(part, (*mine, shard), fup[:, a:b])
-        errors = [float((part.float() - whole[:, a:b].float()).abs().max())]
+        errors = [float((part.detach().float() - whole.detach()[:, a:b].float()).abs().max())]
         errors += [float((g.float() - w[:, a:b].float()).abs().max()) for g, w in zip(part_grads[:3], whole_grads[:3])]
         errors.append(float((part_grads[3].float() - whole_grads[3][:, :, :, a:b].float()).abs().max()))
         worst = torch.tensor(errors, device=device)

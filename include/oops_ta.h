@@ -171,6 +171,34 @@ int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, co
                      const float* lse, const oops_ta_grads* grads, void* stream);
 
 /*
+ * Forward pass with the sigmoid gate of the following output projection applied in the epilogue:
+ * gated = sigmoid(gate) * attention, where `gate` holds the gate logits as a pair tensor of the problem's shape and
+ * dtype.  `plain` (may be NULL or have a NULL ptr) additionally receives the ungated attention values, which the
+ * reverse pass needs (oops_ta_gate_backward, then oops_ta_backward with `plain` as the forward output).  Workspace
+ * and lse as for oops_ta_forward.  The tcgen05 kernels apply the gate to the output tile in registers; the
+ * layout-agnostic kernels run the forward pass and then the element-wise gate.
+ * Fuses the element-wise core of the reference's gate_attention_output (oops/attention/gate/composed.py:47-53,
+ * `sigmoid(linear(single, gate_weight)) * attention`) into the operator that produces its input
+ * (oops/attention/gate/gate_attention_output.py:36-100 consumes triangle attention's output in a pair block).
+ */
+int oops_ta_forward_gated(const oops_ta_problem* problem, const oops_ta_pair* gate, const oops_ta_pair* gated,
+                          const oops_ta_pair* plain, float* lse, void* stream);
+
+/*
+ * The gate on its own: out = sigmoid(gate) * attention for pair tensors (batch, rows, cols, heads, head_dim) with free
+ * strides, and its reverse pass: dattention = dout * sigmoid(gate), dgate = dout * attention * s * (1 - s); a NULL
+ * gradient (or NULL ptr) is skipped.  With strides, the reference's head-major (*, H, Q, D) attention layout and its
+ * token-major (*, Q, H*D) gate layout are the same call (rows = 1, cols = Q).
+ * Replaces the element-wise part of the reference's `project_gate` Triton kernel and of its composed fallback
+ * (oops/attention/gate/composed.py:36-53); the two linear maps around it stay library GEMMs.
+ */
+int oops_ta_gate_forward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair* attention,
+                         const oops_ta_pair* gate, const oops_ta_pair* out, void* stream);
+int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair* attention,
+                          const oops_ta_pair* gate, const oops_ta_pair* dout, const oops_ta_pair* dattention,
+                          const oops_ta_pair* dgate, void* stream);
+
+/*
  * Forward pass that needs no workspace from the caller and allocates nothing.
  *
  * It has no counterpart in the reference.  It is for hosts that cannot hand over scratch memory when

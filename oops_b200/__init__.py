@@ -1,12 +1,14 @@
 """B200-native triangle attention with the call surface of OOps' ``oops`` package.
 
-``import oops_b200 as oops`` gives ``oops.triangle_attention`` and
-``oops.OOpsUnsupportedError`` with the reference's signature and error behaviour
-(``oops/__init__.py:33,73`` in the reference re-exports the same two names).
+``import oops_b200 as oops`` gives ``oops.triangle_attention``, ``oops.gate_attention_output`` and
+``oops.OOpsUnsupportedError`` with the reference's signatures and error behaviour
+(``oops/__init__.py:33,73`` in the reference re-exports the same names), plus
+``oops.triangle_attention_gated``, triangle attention with the gate of the following output
+projection fused into its forward kernel.
 """
 
 from ._errors import OOpsUnsupportedError
-from .attention import triangle_attention
+from .attention import gate_attention_output, triangle_attention, triangle_attention_gated
 from .runtime.nested_tensor import NestedTensor
 
-__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention"]
+__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "triangle_attention_gated"]

@@ -141,6 +141,51 @@ int oops_ta_forward(const oops_ta_problem* problem, const oops_ta_pair* out, flo
   return generic_forward(*problem, *out, lse, s);
 }
 
+int oops_ta_forward_gated(const oops_ta_problem* problem, const oops_ta_pair* gate, const oops_ta_pair* gated,
+                          const oops_ta_pair* plain, float* lse, void* stream) {
+  int status = validate(problem, true);
+  if (status) return status;
+  if (!gate || !gate->ptr || !gated || !gated->ptr) return fail(OOPS_TA_INVALID_ARGUMENT, "gate or gated is NULL");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const oops_ta_pair none{nullptr, 0, 0, 0, 0};
+  const oops_ta_pair& kept = plain && plain->ptr ? *plain : none;
+  if (!force_generic(problem) && tensor_forward_applies(*problem))
+    return tensor_forward_gated(*problem, *gate, *gated, kept, lse, s);
+  // layout-agnostic kernels: the attention values first (into `plain`, or into `gated` itself when the caller
+  // keeps no ungated copy), then the element-wise gate
+  const oops_ta_pair& values = kept.ptr ? kept : *gated;
+  status = generic_forward(*problem, values, lse, s);
+  if (status) return status;
+  return gate_forward(problem->dtype, problem->batch, problem->rows, problem->cols, problem->heads, problem->head_dim, values,
+                      *gate, *gated, s);
+}
+
+int oops_ta_gate_forward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair* attention,
+                         const oops_ta_pair* gate, const oops_ta_pair* out, void* stream) {
+  if (!attention || !attention->ptr || !gate || !gate->ptr || !out || !out->ptr)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "attention, gate or out is NULL");
+  const int status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  return gate_forward(dtype, batch, rows, cols, heads, head_dim, *attention, *gate, *out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair* attention,
+                          const oops_ta_pair* gate, const oops_ta_pair* dout, const oops_ta_pair* dattention,
+                          const oops_ta_pair* dgate, void* stream) {
+  if (!attention || !attention->ptr || !gate || !gate->ptr || !dout || !dout->ptr)
+    return fail(OOPS_TA_INVALID_ARGUMENT, "attention, gate or dout is NULL");
+  const int status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  const oops_ta_pair none{nullptr, 0, 0, 0, 0};
+  return gate_backward(dtype, batch, rows, cols, heads, head_dim, *attention, *gate, *dout, dattention ? *dattention : none,
+                       dgate ? *dgate : none, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, const oops_ta_pair* dout,
                      const float* lse, const oops_ta_grads* grads, void* stream) {
   int status = validate(problem, true);

@@ -41,6 +41,17 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
 int tensor_backward(const oops_ta_problem& p, const oops_ta_pair& out, const oops_ta_pair& dout, const float* lse,
                     const oops_ta_grads& g, cudaStream_t stream);
 
+// Sigmoid gate on attention values and its reverse pass (any strides, f32/f16/bf16); a NULL gradient pointer skips it.
+int gate_forward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair& attention,
+                 const oops_ta_pair& gate, const oops_ta_pair& out, cudaStream_t stream);
+int gate_backward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair& attention,
+                  const oops_ta_pair& gate, const oops_ta_pair& dout, const oops_ta_pair& dattention,
+                  const oops_ta_pair& dgate, cudaStream_t stream);
+// Forward pass of the tcgen05 kernels with the gate applied in the epilogue: writes sigmoid(gate) * out to `gated`
+// and, when plain.ptr is not NULL, the ungated values to `plain`.
+int tensor_forward_gated(const oops_ta_problem& p, const oops_ta_pair& gate, const oops_ta_pair& gated,
+                         const oops_ta_pair& plain, float* lse, cudaStream_t stream);
+
 // Read (and optionally clear) the device-side status words of the two tcgen05 translation units;
 // both synchronise with the device.
 int forward_device_status(int reset);

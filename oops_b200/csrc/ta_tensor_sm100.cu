@@ -69,6 +69,12 @@ struct FwdParams {
   int q_pairs, k_steps;
   int out_vec16;
   float scale;
+  // gated epilogue (GATED instantiations): gated = sigmoid(gate) * out goes to `out`, the ungated values to `plain`
+  const void* gate;
+  int64_t g_sb, g_sr, g_sc, g_sh;
+  void* plain;  // may be null
+  int64_t p_sb, p_sr, p_sc, p_sh;
+  int gate_vec16, plain_vec16;
 };
 
 // The running maximum is only raised when a step exceeds it by more than this (natural-log units):
@@ -76,7 +82,7 @@ struct FwdParams {
 // accumulator rescale (a tensor-memory round trip) is skipped for almost every step.
 constexpr float kRescaleSlack = 5.545177444f;  // 8 * ln 2
 
-template <typename T, bool HAS_BIAS>
+template <typename T, bool HAS_BIAS, bool GATED>
 __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_constant__ FwdParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -430,19 +436,48 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           o2[i] = Half2<T>::pack(__uint_as_float(acc[2 * i]) * inv, __uint_as_float(acc[2 * i + 1]) * inv);
-        T* dst = reinterpret_cast<T*>(P.out) + b * P.o_sb + int64_t(r) * P.o_sr + int64_t(q_index) * P.o_sc + h * P.o_sh;
-        if (P.out_vec16) {
-          uint4* d4 = reinterpret_cast<uint4*>(dst);
+        auto store_row = [&](void* base, int64_t sb, int64_t sr, int64_t sc, int64_t sh, int vec16, const uint32_t (&w)[16]) {
+          T* dst = reinterpret_cast<T*>(base) + b * sb + int64_t(r) * sr + int64_t(q_index) * sc + h * sh;
+          if (vec16) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) d4[i] = make_uint4(o2[4 * i], o2[4 * i + 1], o2[4 * i + 2], o2[4 * i + 3]);
-        } else {
-          unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
+            for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+            unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              d0[2 * i] = (unsigned short)(w[i] & 0xffffu);
+              d0[2 * i + 1] = (unsigned short)(w[i] >> 16);
+            }
+          }
+        };
+        if (GATED) {
+          // The sigmoid gate of the output projection that follows this operator in a pair block, applied to the
+          // 16-bit attention values while they are still in registers: gated = sigmoid(gate) * out.  The ungated
+          // values are stored too when the reverse pass will need them.
+          if (P.plain) store_row(P.plain, P.p_sb, P.p_sr, P.p_sc, P.p_sh, P.plain_vec16, o2);
+          const T* g = reinterpret_cast<const T*>(P.gate) + b * P.g_sb + int64_t(r) * P.g_sr + int64_t(q_index) * P.g_sc + h * P.g_sh;
+          uint32_t gw[16];
+          if (P.gate_vec16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 v = reinterpret_cast<const uint4*>(g)[i];
+              gw[4 * i] = v.x; gw[4 * i + 1] = v.y; gw[4 * i + 2] = v.z; gw[4 * i + 3] = v.w;
+            }
+          } else {
+            const unsigned short* g0 = reinterpret_cast<const unsigned short*>(g);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) gw[i] = uint32_t(g0[2 * i]) | (uint32_t(g0[2 * i + 1]) << 16);
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            d0[2 * i] = (unsigned short)(o2[i] & 0xffffu);
-            d0[2 * i + 1] = (unsigned short)(o2[i] >> 16);
+            // the gate multiplies the attention values as they are returned, i.e. after their 16-bit rounding
+            const float s_lo = 1.f / (1.f + ex2(-Half2<T>::lo(gw[i]) * kLog2e));
+            const float s_hi = 1.f / (1.f + ex2(-Half2<T>::hi(gw[i]) * kLog2e));
+            o2[i] = Half2<T>::pack(Half2<T>::lo(o2[i]) * s_lo, Half2<T>::hi(o2[i]) * s_hi);
           }
         }
+        store_row(P.out, P.o_sb, P.o_sr, P.o_sc, P.o_sh, P.out_vec16, o2);
         if (P.lse) {
           const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
           P.lse[((int64_t(b) * P.rows + r) * P.heads + h) * P.cols + q_index] =
@@ -508,7 +543,14 @@ bool tensor_forward_applies(const oops_ta_problem& p) {
 
 uint64_t tensor_forward_workspace(const oops_ta_problem&) { return 0; }
 
-int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
+namespace {
+
+bool vec16_ok(const oops_ta_pair& t) {
+  return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && t.sb % 8 == 0 && t.sr % 8 == 0 && t.sc % 8 == 0 && t.sh % 8 == 0;
+}
+
+int launch_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, const oops_ta_pair* gate,
+                   const oops_ta_pair* plain, cudaStream_t stream) {
   FwdParams P{};
   int status = encode_pair(&P.map_q, p, p.q, kTile, "query");
   if (!status) status = encode_pair(&P.map_k, p, p.k, kKeys, "key");
@@ -524,8 +566,23 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
   P.o_sr = out.sr;
   P.o_sc = out.sc;
   P.o_sh = out.sh;
-  P.out_vec16 = (reinterpret_cast<uintptr_t>(out.ptr) & 15) == 0 && out.sb % 8 == 0 && out.sr % 8 == 0 &&
-                out.sc % 8 == 0 && out.sh % 8 == 0;
+  P.out_vec16 = vec16_ok(out);
+  if (gate) {
+    P.gate = gate->ptr;
+    P.g_sb = gate->sb;
+    P.g_sr = gate->sr;
+    P.g_sc = gate->sc;
+    P.g_sh = gate->sh;
+    P.gate_vec16 = vec16_ok(*gate);
+    if (plain && plain->ptr) {
+      P.plain = plain->ptr;
+      P.p_sb = plain->sb;
+      P.p_sr = plain->sr;
+      P.p_sc = plain->sc;
+      P.p_sh = plain->sh;
+      P.plain_vec16 = vec16_ok(*plain);
+    }
+  }
   P.lse = lse;
   P.mask = p.mask;
   P.m_sb = p.mask_sb;
@@ -550,9 +607,23 @@ int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse
     count_launch();
     return check_launch("tcgen05 forward");
   };
-  if (p.dtype == OOPS_TA_BF16)
-    return has_bias ? launch(ta_fwd_kernel<__nv_bfloat16, true>) : launch(ta_fwd_kernel<__nv_bfloat16, false>);
-  return has_bias ? launch(ta_fwd_kernel<__half, true>) : launch(ta_fwd_kernel<__half, false>);
+  auto pick = [&](auto type_tag) -> int {
+    using T = decltype(type_tag);
+    if (gate) return has_bias ? launch(ta_fwd_kernel<T, true, true>) : launch(ta_fwd_kernel<T, false, true>);
+    return has_bias ? launch(ta_fwd_kernel<T, true, false>) : launch(ta_fwd_kernel<T, false, false>);
+  };
+  return p.dtype == OOPS_TA_BF16 ? pick(__nv_bfloat16{}) : pick(__half{});
+}
+
+}  // namespace
+
+int tensor_forward(const oops_ta_problem& p, const oops_ta_pair& out, float* lse, cudaStream_t stream) {
+  return launch_forward(p, out, lse, nullptr, nullptr, stream);
+}
+
+int tensor_forward_gated(const oops_ta_problem& p, const oops_ta_pair& gate, const oops_ta_pair& gated,
+                         const oops_ta_pair& plain, float* lse, cudaStream_t stream) {
+  return launch_forward(p, gated, lse, &gate, &plain, stream);
 }
 
 int forward_device_status(int reset) { return read_tu_device_status(reset); }

@@ -80,3 +80,25 @@ def test_nested_golden():
 def test_flops_formula():
     assert oracle.flops(1, 768, 768, 4, 32, backward=True) == pytest.approx(8.117e11, rel=1e-3)
     assert oracle.flops(1, 2048, 2048, 4, 32, backward=False) == pytest.approx(4.398e12, rel=1e-3)
+
+
+@pytest.mark.parametrize("name", ["f32_rank4", "f64_rank3", "f32_rank5"])
+def test_gate_oracle_matches_the_reference_statement(name):
+    """The gate oracle against outputs and autograd gradients of the reference's own `_reference`
+    (tests/attention/gate/test_gate_attention_output.py:40-43), stored in tests/golden/gate.pt."""
+    from oracle import gate_oracle
+
+    case = torch.load(GOLDEN / "gate.pt", weights_only=False)[name]
+    dtype = case["attention"].dtype
+    leaves = [case[n].clone().requires_grad_(True) for n in ("attention", "single", "gate_weight", "output_weight")]
+    out = gate_oracle.gate_attention_output(*leaves, compute_dtype=dtype)
+    tol = dict(atol=1e-10, rtol=1e-10) if dtype is torch.float64 else dict(atol=2e-6, rtol=1e-5)
+    torch.testing.assert_close(out, case["out"], **tol)
+    for got, want in zip(torch.autograd.grad(out, leaves, case["upstream"]), case["grads"]):
+        torch.testing.assert_close(got, want, **tol)
+    # the element-wise core alone, in the token-major layout the fused epilogue works in
+    attention, single, gate_weight, output_weight = (case[n] for n in ("attention", "single", "gate_weight", "output_weight"))
+    *prefix, heads, length, head_size = attention.shape
+    token_major = attention.transpose(-3, -2).reshape(*prefix, length, heads * head_size)
+    gated = gate_oracle.gated_values(token_major, torch.nn.functional.linear(single, gate_weight), compute_dtype=dtype)
+    torch.testing.assert_close(torch.nn.functional.linear(gated, output_weight), case["out"], **tol)
