@@ -557,10 +557,34 @@ def main():
         with torch.no_grad():
             ms3f = timed(lambda: triangle_attention(q3, k3, v3, m3, b3), max(args.steps, 10))
         f3, f3f = flops(n3, n3, heads, dim, True), flops(n3, n3, heads, dim, False)
+        # the gate of the following output projection, fused into the forward epilogue or applied as its own pass
+        from oops_b200 import triangle_attention_gated
+        from oops_b200.attention.gate.gate_attention_output import _run_gate
+
+        gate3 = torch.randn(q3.shape, dtype=q3.dtype, device=device)
+        with torch.no_grad():
+            fused = lambda: triangle_attention_gated(q3, k3, v3, gate3, m3, b3)  # noqa: E731
+
+            def unfused():
+                values = triangle_attention(q3, k3, v3, m3, b3)
+                gated = torch.empty_like(values)
+                _run_gate(values, gate3, gated)
+                return gated
+
+            for _ in range(3):
+                fused(), unfused()
+            ms_fused, ms_unfused = timed(fused, max(args.steps, 10)), timed(unfused, max(args.steps, 10))
+        pass_bytes = q3.numel() * q3.element_size()
+        gated_entry = {
+            "fused_forward_ms": ms_fused, "forward_then_gate_kernel_ms": ms_unfused,
+            "saved_hbm_bytes": 2 * pass_bytes,  # the attention values are neither written nor read back
+            "note": "inference, N=768: sigmoid(gate) * attention in the forward kernel's epilogue against the forward "
+                    "kernel followed by the library's element-wise gate kernel",
+        }
         line["n768"] = {
             "workload": WORKLOADS["cfg3"]["label"], "fwd_bwd_ms": ms3, "fwd_bwd_tflops": f3 / ms3 / 1e9,
             "fwd_bwd_frac_of_bf16_peak": f3 / ms3 / 1e9 / peak, "fwd_ms": ms3f, "fwd_tflops": f3f / ms3f / 1e9,
-            "fwd_frac_of_bf16_peak": f3f / ms3f / 1e9 / peak,
+            "fwd_frac_of_bf16_peak": f3f / ms3f / 1e9 / peak, "gated_output": gated_entry,
         }
 
     # a kernel that gave up a bounded wait leaves undefined results: none may have
