@@ -1559,23 +1559,16 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
-      // The row's 32 logits of this thread in four rounds of eight tensor-memory columns.  Rows with a dropped key
-      // take a second copy of the body that zeroes the dropped columns: a test per element inside one body would
-      // be compiled into selects that every row pays for.
+      // The row's 32 logits of this thread, four tensor-memory columns of S and of dP at a time.  Rows with a dropped
+      // key take a second copy of the body that zeroes the dropped columns: a test per element inside one body
+      // would be compiled into selects that every row pays for.
       auto row_body = [&](auto drops_keys) {
+        // two pairs (four tensor-memory columns of S and of dP) at a time; the loads of the next four columns are in
+        // flight while the current four are worked on
+        auto work4 = [&](int quad, const uint32_t (&sraw)[4], const uint32_t (&draw)[4]) {
 #pragma unroll
-        for (int round = 0; round < 4; ++round) {
-          uint32_t sraw[8], draw[8];
-          tmem_ld8(s_t + round * 8, sraw);
-          tmem_ld8(s_t + kTile + round * 8, draw);
-          tmem_wait_ld();
-          if (round == 3) {
-            tc_fence_before_sync();
-            mbar_arrive_warp(bar(DbSmem::sd_free + buf));
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int pair = round * 4 + j;
+          for (int j = 0; j < 2; ++j) {
+            const int pair = quad * 2 + j;
             const f32x2 s2 = pack2(__uint_as_float(sraw[2 * j]), __uint_as_float(sraw[2 * j + 1]));
             const f32x2 d2 = pack2(__uint_as_float(draw[2 * j]), __uint_as_float(draw[2 * j + 1]));
             f32x2 p;
@@ -1594,12 +1587,30 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
             }
             f32x2 dd = add2(d2, nd1);
             if (decltype(drops_keys)::value) {
-              // a dropped key's row of K or V may hold anything, so its S and dP may be non-finite: both factors go to zero
               p = select2(p, bits, 2 * pair);
               dd = select2(dd, bits, 2 * pair);
             }
             acc2[pair] = fma2(p, dd, acc2[pair]);
           }
+        };
+        uint32_t s_a[4], d_a[4], s_b[4], d_b[4];
+        tmem_ld4(s_t, s_a);
+        tmem_ld4(s_t + kTile, d_a);
+#pragma unroll
+        for (int quad = 0; quad < 8; quad += 2) {
+          tmem_wait_ld();
+          tmem_ld4(s_t + (quad + 1) * 4, s_b);
+          tmem_ld4(s_t + kTile + (quad + 1) * 4, d_b);
+          work4(quad, s_a, d_a);
+          tmem_wait_ld();
+          if (quad + 2 < 8) {
+            tmem_ld4(s_t + (quad + 2) * 4, s_a);
+            tmem_ld4(s_t + kTile + (quad + 2) * 4, d_a);
+          } else {
+            tc_fence_before_sync();
+            mbar_arrive_warp(bar(DbSmem::sd_free + buf));
+          }
+          work4(quad + 1, s_b, d_b);
         }
       };
       if (bits == 0xffffffffu)
