@@ -424,6 +424,14 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       mbar_arrive_warp(bar(FwdSmem::p_full + w));
     }
 
+    // Gated epilogue: the thread's 32 gate logits are requested before the wait for the last product, so that their
+    // trip from global memory runs under it (the words are not touched until the output row is ready).
+    uint4 gate_words[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (GATED && P.gate_vec16 && ok && q_index < P.cols) {
+      const T* g = reinterpret_cast<const T*>(P.gate) + b * P.g_sb + int64_t(r) * P.g_sr + int64_t(q_index) * P.g_sc + h * P.g_sh;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gate_words[i] = ldg_v4_here_if(reinterpret_cast<const uint4*>(g) + i, true);
+    }
     if (ok) ok = mbar_wait(bar(FwdSmem::o_final + w), 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
@@ -461,7 +469,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
           if (P.gate_vec16) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 v = reinterpret_cast<const uint4*>(g)[i];
+              const uint4 v = gate_words[i];
               gw[4 * i] = v.x; gw[4 * i + 1] = v.y; gw[4 * i + 2] = v.z; gw[4 * i + 3] = v.w;
             }
           } else {
@@ -472,8 +480,8 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             // the gate multiplies the attention values as they are returned, i.e. after their 16-bit rounding
-            const float s_lo = 1.f / (1.f + ex2(-Half2<T>::lo(gw[i]) * kLog2e));
-            const float s_hi = 1.f / (1.f + ex2(-Half2<T>::hi(gw[i]) * kLog2e));
+            const float s_lo = rcp(1.f + ex2(-Half2<T>::lo(gw[i]) * kLog2e));
+            const float s_hi = rcp(1.f + ex2(-Half2<T>::hi(gw[i]) * kLog2e));
             o2[i] = Half2<T>::pack(Half2<T>::lo(o2[i]) * s_lo, Half2<T>::hi(o2[i]) * s_hi);
           }
         }

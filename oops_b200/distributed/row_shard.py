@@ -209,4 +209,96 @@ def row_sharded_triangle_attention(
     return _RowShardedAttention.apply(q5, k5, v5, mask3, bias_shard, scale, group, _flags())
 
 
-__all__ = ["shard_bounds", "gather_bias", "row_sharded_triangle_attention"]
+# ----------------------------------------------------------------------------------------------
+# ending-node form under row sharding
+# ----------------------------------------------------------------------------------------------
+
+
+def _exchange_pair_axes(x: Tensor, group, rows_to_cols: bool) -> Tensor:
+    """All-to-all between the two shardings of a pair tensor whose axes 1 and 2 are (row, column).
+
+    ``rows_to_cols``: this rank's rows ``(B, R/P, C, *tail)`` become this rank's columns of all rows
+    ``(B, R, C/P, *tail)``; otherwise the inverse.  Rank p owns the p-th contiguous block of the sharded axis."""
+    world = dist.get_world_size(group)
+    batch, a, b = x.shape[:3]
+    tail = tuple(x.shape[3:])
+    if rows_to_cols:
+        if b % world != 0:
+            raise ValueError(f"columns={b} must be divisible by the number of ranks ({world})")
+        # piece for rank p: my rows, its block of columns
+        send = x.reshape(batch, a, world, b // world, *tail).movedim(2, 0).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        # received piece p: rank p's rows, my block of columns
+        return recv.movedim(0, 1).reshape(batch, world * a, b // world, *tail)
+    if a % world != 0:
+        raise ValueError(f"rows={a} must be divisible by the number of ranks ({world})")
+    # piece for rank p: its block of rows, my columns
+    send = x.reshape(batch, world, a // world, b, *tail).movedim(1, 0).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # received piece p: my rows, rank p's block of columns
+    return recv.movedim(0, 2).reshape(batch, a // world, world * b, *tail)
+
+
+class _ExchangePairAxes(torch.autograd.Function):
+    """Differentiable re-shard: the reverse pass is the inverse exchange of the gradient."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group, rows_to_cols: bool) -> Tensor:
+        ctx.group, ctx.rows_to_cols = group, rows_to_cols
+        return _exchange_pair_axes(x, group, rows_to_cols)
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        return _exchange_pair_axes(grad.contiguous(), ctx.group, not ctx.rows_to_cols), None, None
+
+
+def reshard_rows_to_columns(x: Tensor, group=None) -> Tensor:
+    """``(B, R/P, C, ...)`` (this rank's rows) -> ``(B, R, C/P, ...)`` (this rank's columns); differentiable."""
+    return _ExchangePairAxes.apply(x, group, True)
+
+
+def reshard_columns_to_rows(x: Tensor, group=None) -> Tensor:
+    """``(B, R, C/P, ...)`` (this rank's columns) -> ``(B, R/P, C, ...)`` (this rank's rows); differentiable."""
+    return _ExchangePairAxes.apply(x, group, False)
+
+
+def row_sharded_ending_node_attention(
+    query: Tensor,
+    key: Tensor,
+    value: Tensor,
+    mask: Optional[Tensor] = None,
+    bias_shard: Optional[Tensor] = None,
+    *,
+    scale: Optional[float] = None,
+    group=None,
+    attention: Callable = triangle_attention,
+) -> Tensor:
+    """Ending-node triangle attention for a pair tensor that is sharded by rows.
+
+    The ending-node form attends along the *row* axis (the operator is called on the pair-axes transpose), so its
+    softmax runs along the sharded axis: the pair tensors are first re-sharded to column ownership with one
+    all-to-all each, the local call then runs on the transposed views (this rank's columns are its independent
+    softmax domains; nothing is copied for the transpose, the kernels read the swapped strides), and the result is
+    re-sharded back to rows.  No counterpart in the reference, which has no multi-GPU code.
+
+    Args:
+        query, key, value: this rank's rows ``(B, R/P, C, H, D)`` of the square pair tensors (R = C).
+        mask: this rank's rows ``(B, R/P, C)`` of the keep-mask of the pair cells.
+        bias_shard: this rank's query rows ``(B, 1, H, R/P, R)`` of the bias of the ending-node operator.
+
+    Returns this rank's rows of the result, ``(B, R/P, C, H, D)``.
+    """
+    q, k, v = (reshard_rows_to_columns(t, group).transpose(1, 2) for t in (query, key, value))
+    m = None
+    if mask is not None:
+        m = _exchange_pair_axes(mask.expand(query.shape[:3]).contiguous(), group, True).transpose(1, 2)
+    out = row_sharded_triangle_attention(q, k, v, m, bias_shard, scale=scale, group=group, attention=attention)
+    return reshard_columns_to_rows(out.transpose(1, 2), group)
+
+
+__all__ = [
+    "shard_bounds", "gather_bias", "row_sharded_triangle_attention", "reshard_rows_to_columns", "reshard_columns_to_rows",
+    "row_sharded_ending_node_attention",
+]

@@ -80,3 +80,45 @@ def test_shard_bounds():
         pass
     else:
         raise AssertionError("uneven shards must be rejected")
+
+
+def _ending_worker(rank: int, world: int, port: int, results):
+    from oops_b200.distributed.row_shard import row_sharded_ending_node_attention
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q, k, v, bias, mask, upstream = _inputs()
+        lo, hi = shard_bounds(q.shape[1], world, rank)
+        leaves = [t[:, lo:hi].clone().requires_grad_(True) for t in (q, k, v)]
+        bias_shard = bias[:, :, :, lo:hi].clone().requires_grad_(True)
+
+        def local(query, key, value, m, b, scale=None):
+            return oracle.reference_dense(query, key, value, m, b, scale)
+
+        out = row_sharded_ending_node_attention(*leaves, mask[:, lo:hi], bias_shard, attention=local)
+        grads = torch.autograd.grad(out, [*leaves, bias_shard], upstream[:, lo:hi])
+        results[rank] = [out.detach()] + [g.detach() for g in grads]
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ending_node_reshard_matches_unsharded():
+    """Ending-node attention on a row-sharded pair tensor: re-shard to columns, attend on the transposed views,
+    re-shard back; equals the unsharded ending-node call (the operator on the pair-axes transpose)."""
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_ending_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    q, k, v, bias, mask, upstream = _inputs()
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, bias)]
+    out = oracle.reference_dense(leaves[0].transpose(1, 2), leaves[1].transpose(1, 2), leaves[2].transpose(1, 2),
+                                 mask.transpose(1, 2), leaves[3]).transpose(1, 2)
+    want = [out.detach(), *torch.autograd.grad(out, leaves, upstream)]
+    for rank in range(world):
+        lo, hi = shard_bounds(q.shape[1], world, rank)
+        got = results[rank]
+        for name, g, w in zip(("out", "dq", "dk", "dv"), got[:4], want[:4]):
+            torch.testing.assert_close(g, w[:, lo:hi], atol=1e-5, rtol=1e-5, msg=lambda m, name=name: f"{name}: {m}")
+        torch.testing.assert_close(got[4], want[4][:, :, :, lo:hi], atol=1e-5, rtol=1e-5)
