@@ -45,6 +45,10 @@ WORKLOADS = {
     # name: (N, heads, head_dim) -- BASELINE configs 5 and 3
     "cfg5": dict(n=2048, heads=4, dim=32, label="config 5: starting node, bf16, fwd+bwd, B=1, N=2048, H=4, D=32"),
     "cfg3": dict(n=768, heads=4, dim=32, label="config 3: starting node, bf16, fwd+bwd, B=1, N=768, H=4, D=32"),
+    # the remaining BASELINE configurations: timed device-resident on one GPU, short line (no roofline / e2e legs)
+    "cfg1": dict(n=64, heads=4, dim=32, label="config 1: starting node, f32, fwd+bwd, B=1, N=64, H=4, D=32"),
+    "cfg2": dict(n=384, heads=4, dim=32, label="config 2: starting node, bf16, fwd only, B=1, N=384 (350 valid), H=4, D=32"),
+    "cfg4": dict(n=1024, heads=4, dim=32, label="config 4: ending node, bf16, fwd+bwd, ragged batch of 1024 and 700 tokens, H=4, D=32"),
 }
 FALLBACK_PEAK_TFLOPS = 1590.0
 METRIC = "triangle_attention_fwd_bwd_tflops"
@@ -118,13 +122,14 @@ class ClockSampler:
         }
 
 
-def make_inputs(n, heads, dim, row_lo, row_hi, seed):
-    """Synthetic inputs of the configuration for rows [row_lo, row_hi): N(0,1)*0.5 q/k/v, N(0,1) bias and upstream."""
+def make_inputs(n, heads, dim, row_lo, row_hi, seed, bias_rows=None):
+    """Synthetic inputs of the configuration for rows [row_lo, row_hi): N(0,1)*0.5 q/k/v, N(0,1) bias and upstream.
+    `bias_rows` query rows of the bias are made (default: as many as pair rows, the rank's shard of a square bias)."""
     gen = torch.Generator().manual_seed(seed)
     rows = row_hi - row_lo
     q, k, v = ((torch.randn(1, rows, n, heads, dim, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(3))
     upstream = torch.randn(1, rows, n, heads, dim, generator=gen).to(torch.bfloat16)
-    bias_shard = torch.randn(1, 1, heads, rows, n, generator=gen).to(torch.bfloat16)  # query rows [row_lo, row_hi)
+    bias_shard = torch.randn(1, 1, heads, bias_rows or rows, n, generator=gen).to(torch.bfloat16)  # the rank's query rows
     mask = torch.ones(1, rows, n, dtype=torch.bool)
     return q, k, v, upstream, bias_shard, mask
 
@@ -338,6 +343,94 @@ class StreamedStep:
         self._keep = (keep, final, bias)
 
 
+def small_workload(args, work):
+    """Configurations 1, 2 and 4: device-resident forward and forward+backward times on one GPU."""
+    from oops_b200 import NestedTensor, triangle_attention
+    from oops_b200.runtime import cabi
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    heads, dim, n = work["heads"], work["dim"], work["n"]
+    gen = torch.Generator().manual_seed(0)
+    name = args.workload
+    if name == "cfg4":
+        lengths = (1024, 700)
+        stored = {k: [(torch.randn(L, L, heads, dim, generator=gen) * 0.5).to(torch.bfloat16) for L in lengths] for k in "qkv"}
+        biases = [torch.randn(1, heads, L, L, generator=gen).to(torch.bfloat16) for L in lengths]
+        tokens = [torch.rand(L, generator=gen) > 0.1 for L in lengths]
+        masks = [tok[:, None] & tok[None, :] for tok in tokens]
+        leaves, operands = [], []
+        for k in "qkv":
+            template = NestedTensor(stored[k], ragged_dims=(0, 1))
+            values = template.concat.to(device).requires_grad_(True)
+            leaves.append(values)
+            operands.append(template.packed_like(values).transpose(-4, -3))
+        mask_template = NestedTensor(masks, ragged_dims=(0, 1))
+        operands.append(mask_template.packed_like(mask_template.concat.to(device)).transpose(-2, -1))
+        bias_template = NestedTensor(biases, ragged_dims=(2, 3))
+        bias_values = bias_template.concat.to(device).requires_grad_(True)
+        leaves.append(bias_values)
+        operands.append(bias_template.packed_like(bias_values).transpose(-2, -1))
+        upstream = torch.randn(leaves[0].shape, generator=gen).to(torch.bfloat16).to(device)
+        call = lambda: triangle_attention(*operands).concat  # noqa: E731
+        scores = float(sum(L**3 for L in lengths)) * heads
+        backward = True
+    else:
+        dtype = torch.float32 if name == "cfg1" else torch.bfloat16
+        scale_in = 1.0 if name == "cfg1" else 0.5
+        q, k, v = ((torch.randn(1, n, n, heads, dim, generator=gen) * scale_in).to(dtype).to(device).requires_grad_(True) for _ in range(3))
+        bias = torch.randn(1, 1, heads, n, n, generator=gen).to(dtype).to(device).requires_grad_(True)
+        upstream = torch.randn(1, n, n, heads, dim, generator=gen).to(dtype).to(device)
+        valid = 350 if name == "cfg2" else n
+        tok = torch.arange(n) < valid
+        mask = (tok[:, None] & tok[None, :])[None].to(device)
+        leaves = [q, k, v, bias]
+        call = lambda: triangle_attention(q, k, v, mask, bias)  # noqa: E731
+        scores = float(n) ** 3 * heads
+        backward = name != "cfg2"
+
+    def timed(fn, iters):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / iters
+
+    def step():
+        out = call()
+        if backward:
+            torch.autograd.grad(out, leaves, upstream)
+
+    iters = max(args.steps, 20)
+    for _ in range(max(3, args.warmup)):
+        step()
+    before = cabi.launch_count()
+    ms_step = timed(step, iters)
+    launches = cabi.launch_count() - before
+    with torch.no_grad():
+        for _ in range(3):
+            call()
+        ms_fwd = timed(call, iters)
+    peak, _, _ = measured_peak()
+    total = scores * dim * (14.0 if backward else 4.0)
+    status = cabi.device_status(reset=False)
+    if status != 0:
+        raise SystemExit(f"a kernel recorded device status {status}; the measurements above are void")
+    line = {
+        "metric": METRIC if backward else "triangle_attention_fwd_tflops", "value": total / (ms_step * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": iters, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if name == "cfg1" else "bf16",
+        "data": "synthetic", "config": {"workload": work["label"], "l2": "inputs fit in L2 at this size (no flush): a small-problem latency figure"
+                                        if name in ("cfg1", "cfg2") else "inputs larger than L2 (no flush needed)"},
+        "fwd": {"ms": ms_fwd, "tflops": scores * dim * 4.0 / (ms_fwd * 1e-3) / 1e12},
+        "frac_of_bf16_peak": total / (ms_step * 1e-3) / 1e12 / peak, "gpu_launches": int(launches),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -347,6 +440,9 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference", "reference-gpu"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-extra", action="store_true", help="skip the secondary N=768 measurement")
+    parser.add_argument("--rows", type=int, default=0,
+                        help="time only the first ROWS pair rows of each GPU's shard (a slice for profiler captures; "
+                             "rows are independent, FLOPs are counted for the slice)")
     parser.add_argument("--with-reference-gpu", action="store_true",
                         help="also time the reference's own GPU operator (a child process) and report it beside ours")
     args = parser.parse_args()
@@ -356,6 +452,11 @@ def main():
         return
     if args.impl == "reference-gpu":
         reference_gpu_arm(args, work)
+        return
+    if args.workload in ("cfg1", "cfg2", "cfg4"):
+        if args.gpus != 1:
+            raise SystemExit("configurations 1, 2 and 4 are single-GPU workloads")
+        small_workload(args, work)
         return
 
     import torch.distributed as dist
@@ -380,6 +481,9 @@ def main():
 
     n, heads, dim = work["n"], work["heads"], work["dim"]
     lo, hi = shard_bounds(n, world, rank)
+    if args.rows:
+        hi = min(hi, lo + args.rows)
+    total_rows = (hi - lo) * world
 
     def step(q, k, v, bias_shard, mask, upstream):
         if distributed:
@@ -434,7 +538,7 @@ def main():
             raise SystemExit(f"row-sharded results differ from the unsharded call: {parity}")
         del full, leaves, whole, whole_grads, mine, shard, part, part_grads
 
-    host = [t.pin_memory() for t in make_inputs(n, heads, dim, lo, hi, seed=100 + rank)]
+    host = [t.pin_memory() for t in make_inputs(n, heads, dim, lo, hi, seed=100 + rank, bias_rows=n // world)]
     q, k, v, upstream, bias_shard, mask = (t.to(device) for t in host)
     q, k, v, bias_shard = (t.requires_grad_(True) for t in (q, k, v, bias_shard))
 
@@ -447,7 +551,7 @@ def main():
     launches = torch.tensor([cabi.launch_count() - launches_before], device=device, dtype=torch.int64)
     if distributed:
         dist.all_reduce(launches)
-    total_flops = flops(n, n, heads, dim, True)
+    total_flops = flops(total_rows, n, heads, dim, True)
     value = total_flops / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: every input in from pinned host memory, every result out, every step ----
@@ -460,7 +564,30 @@ def main():
     streamed()
     ms_e2e = timed(streamed, e2e_iters)
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+    # the host link on its own: the step's copies without any kernel, one direction at a time and both at once
+    def copies(inbound, outbound):
+        def run():
+            main_stream = torch.cuda.current_stream(device)
+            streamed.s_in.wait_stream(main_stream)
+            streamed.s_out.wait_stream(main_stream)
+            if inbound:
+                with torch.cuda.stream(streamed.s_in):
+                    for dst, src in zip(link_in, (streamed.q, streamed.k, streamed.v, streamed.up)):
+                        dst.copy_(src, non_blocking=True)
+            if outbound:
+                with torch.cuda.stream(streamed.s_out):
+                    for dst, src in zip(streamed.out, link_in):
+                        dst.copy_(src, non_blocking=True)
+            main_stream.wait_stream(streamed.s_in)
+            main_stream.wait_stream(streamed.s_out)
+        return run
+
+    link_in = [torch.empty(streamed.q.shape, dtype=streamed.q.dtype, device=device) for _ in range(4)]
+    link = {name: timed(copies(*flags), 2) for name, flags in (("h2d_only_ms", (True, False)), ("d2h_only_ms", (False, True)),
+                                                                ("both_directions_ms", (True, True)))}
+    del link_in
     e2e = {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": streamed.h2d_bytes * world,
+           "host_link": link,
            "d2h_bytes_per_step": streamed.d2h_bytes * world, "row_blocks": len(streamed.blocks),
            "results_copied_back": ["out", "dq", "dk", "dv", "dbias"]}
     del streamed
@@ -525,7 +652,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "workload": work["label"], "rows_per_gpu": hi - lo, "sharding": "pair rows; bias all-gather, dbias reduce-scatter"
+            "workload": work["label"] + (f" (slice: {hi - lo} rows per GPU)" if args.rows else ""), "rows_per_gpu": hi - lo, "sharding": "pair rows; bias all-gather, dbias reduce-scatter"
             if distributed else "single GPU", "l2": "inputs larger than L2 (no flush needed)",
             "tensor_path": {"forward": None, "backward": None},
         },
