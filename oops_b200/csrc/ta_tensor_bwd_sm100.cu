@@ -934,7 +934,7 @@ static_assert(kFSmemBytes <= 232448, "fused reverse kernel: shared memory over t
 struct FParams {
   CUtensorMap map_q, map_dout, map_k, map_v, map_bias;
   oops_ta_pair dq, dk, dv;
-  float* slots;     // [kFSlots][2][slot_keys][32] f32: sums of dK and dV carried from group to group (groups > 1)
+  float* slots;     // [kFSlots][2][8][slot_keys][4] f32: sums of dK and dV carried from group to group (groups > 1)
   int64_t slot_keys;
   const float* lse;
   const float* delta;
@@ -1081,17 +1081,17 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       }
     }
   } else if (warp == kFScoreWarp) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = instr_desc(Half2<T>::kFormat, 0, 0, kTile, kTile);
       bool ok = true;
       for (FWalk w(P); !w.done() && ok; w.next()) {
         const int s = w.s, qs = s % 3, ks = w.ktc & 1;
-        ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
+        ok = mbar_wait_warp(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
         if (ok && w.qi == 0) {
-          ok = mbar_wait(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
-          if (ok && signoff) ok = mbar_wait(bar(FSmem::k_ready + ks), (w.ktc >> 1) & 1, abort_flag);
+          ok = mbar_wait_warp(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
+          if (ok && signoff) ok = mbar_wait_warp(bar(FSmem::k_ready + ks), (w.ktc >> 1) & 1, abort_flag);
         }
-        if (ok && s > 0) ok = mbar_wait(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
+        if (ok && s > 0) ok = mbar_wait_warp(bar(FSmem::sd_free), (s - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint64_t qdesc = smem_desc(smem_base + FSmem::q + qs * kBigTile, 16, 512, kSwizzle64B);
@@ -1100,28 +1100,28 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         const uint64_t vdesc = smem_desc(smem_base + FSmem::v + ks * kBigTile, 16, 512, kSwizzle64B);
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          mma_ss(tmem_base + kSCol, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+          mma_ss_warp(tmem_base + kSCol, qdesc + uint64_t(kk * 2), kdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          mma_ss(tmem_base + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
-        mma_commit(bar(FSmem::sd_full));
+          mma_ss_warp(tmem_base + kDpCol, ddesc + uint64_t(kk * 2), vdesc + uint64_t(kk * 2), idesc, kk > 0 ? 1u : 0u);
+        mma_commit_warp(bar(FSmem::sd_full));
       }
     }
   } else if (warp == kFAccWarp) {
-    if (lane == 0) {
+    {
       constexpr uint32_t fmt = Half2<T>::kFormat;
       constexpr uint32_t idesc_t = instr_desc(fmt, 1, 1, kTile, kHeadDim);  // A = image^T (M = keys), B MN-major
       constexpr uint32_t idesc_q = instr_desc(fmt, 0, 1, kTile, kHeadDim);  // A = image (M = queries), B MN-major
       bool ok = true;
       for (FWalk w(P); !w.done() && ok; w.next()) {
         const int s = w.s, kt = w.kt, qi = w.qi, qs = s % 3, ks = w.ktc & 1;
-        ok = mbar_wait(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
-        if (ok) ok = mbar_wait(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
-        if (ok) ok = mbar_wait(bar(FSmem::pds_full + (s & 1)), (s >> 1) & 1, abort_flag);
+        ok = mbar_wait_warp(bar(FSmem::qd_full + qs), (s / 3) & 1, abort_flag);
+        if (ok) ok = mbar_wait_warp(bar(FSmem::kv_full + ks), (w.ktc >> 1) & 1, abort_flag);
+        if (ok) ok = mbar_wait_warp(bar(FSmem::pds_full + (s & 1)), (s >> 1) & 1, abort_flag);
         // dK and dV of the previous key tile must have been read out before they are overwritten,
         // and so must dQ of the previous group of query tiles
-        if (ok && qi == 0 && w.ktc > 0) ok = mbar_wait(bar(FSmem::dkv_free), (w.ktc - 1) & 1, abort_flag);
-        if (ok && qi == 0 && kt == 0 && w.g > 0) ok = mbar_wait(bar(FSmem::dq_free), (w.g - 1) & 1, abort_flag);
+        if (ok && qi == 0 && w.ktc > 0) ok = mbar_wait_warp(bar(FSmem::dkv_free), (w.ktc - 1) & 1, abort_flag);
+        if (ok && qi == 0 && kt == 0 && w.g > 0) ok = mbar_wait_warp(bar(FSmem::dq_free), (w.g - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t ps = smem_base + FSmem::ps, dss = smem_base + FSmem::dss + (s & 1) * kFImage;
@@ -1130,20 +1130,20 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         const uint64_t kdesc = smem_desc(smem_base + FSmem::k + ks * kBigTile, 16, 512, kSwizzle64B);       // MN-major B
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)  // dV[128 k x 32] += P^T[128 k x 128 q] dO[128 q x 32]
-          mma_ss(tmem_base + kDvCol, smem_desc(ps + kk * 2048, 16384, 1024, kSwizzle128B), ddesc + uint64_t(kk * (1024 >> 4)),
+          mma_ss_warp(tmem_base + kDvCol, smem_desc(ps + kk * 2048, 16384, 1024, kSwizzle128B), ddesc + uint64_t(kk * (1024 >> 4)),
                  idesc_t, (qi > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(bar(FSmem::p_done));
+        mma_commit_warp(bar(FSmem::p_done));
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)  // dK[128 k x 32] += dS^T[128 k x 128 q] Q[128 q x 32]
-          mma_ss(tmem_base + kDkCol, smem_desc(dss + kk * 2048, 16384, 1024, kSwizzle128B), qdesc + uint64_t(kk * (1024 >> 4)),
+          mma_ss_warp(tmem_base + kDkCol, smem_desc(dss + kk * 2048, 16384, 1024, kSwizzle128B), qdesc + uint64_t(kk * (1024 >> 4)),
                  idesc_t, (qi > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)  // dQ[128 q x 32] += dS[128 q x 128 k] K[128 k x 32]
-          mma_ss(tmem_base + kDqCol + qi * kHeadDim, smem_desc(dss + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, kSwizzle128B),
+          mma_ss_warp(tmem_base + kDqCol + qi * kHeadDim, smem_desc(dss + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, kSwizzle128B),
                  kdesc + uint64_t(kk * (1024 >> 4)), idesc_q, (kt > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(bar(FSmem::pds_done + (s & 1)));
-        mma_commit(bar(FSmem::qd_empty + qs));
-        if (qi == w.nq - 1) mma_commit(bar(FSmem::kv_empty + ks));
+        mma_commit_warp(bar(FSmem::pds_done + (s & 1)));
+        mma_commit_warp(bar(FSmem::qd_empty + qs));
+        if (qi == w.nq - 1) mma_commit_warp(bar(FSmem::kv_empty + ks));
       }
     }
   } else if (warp < 16) {
@@ -1181,24 +1181,20 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       const bool wanted = wg == 0 ? P.write_dk != 0 : P.write_dv != 0;
       if (!wanted) return;
       if (P.groups > 1) {
-        float4* slot = reinterpret_cast<float4*>(P.slots + ((int64_t(sm_id) * 2 + wg) * P.slot_keys + key) * kHeadDim);
-        if (g > 0) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 carried = slot[i];
-            acc[4 * i] = __float_as_uint(__uint_as_float(acc[4 * i]) + carried.x);
-            acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + carried.y);
-            acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + carried.z);
-            acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + carried.w);
-          }
-        }
-        if (g < P.groups - 1) {
+        // plane i of the slot holds channels 4i .. 4i+3 of every key, so that a warp's 32 keys are 512 contiguous bytes
+        float4* slot = reinterpret_cast<float4*>(P.slots) + (int64_t(sm_id) * 2 + wg) * 8 * P.slot_keys + key;
+        if (g == 0) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            slot[i] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]), __uint_as_float(acc[4 * i + 2]),
-                                  __uint_as_float(acc[4 * i + 3]));
-          return;
+            slot[i * P.slot_keys] = make_float4(__uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                                                __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            red_add_f4(slot + i * P.slot_keys, __uint_as_float(acc[4 * i]), __uint_as_float(acc[4 * i + 1]),
+                       __uint_as_float(acc[4 * i + 2]), __uint_as_float(acc[4 * i + 3]));
         }
+        return;
       }
       const oops_ta_pair& o = wg == 0 ? P.dk : P.dv;
       T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh;
@@ -1236,6 +1232,11 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     int last_g = 0, last_kt = 0;  // group and key tile of the previous step
     for (; !w.done() && ok; last_g = w.g, last_kt = w.kt, w.next()) {
       const int s = w.s, kt = w.kt, qi = w.qi, buf = s & 1;
+      // The three phases the step needs first are probed together (one round trip to the barrier words); in the steady
+      // state, where these warps are the slow side of the pipeline, all three are complete.
+      const bool bias_there = HAS_BIAS && mbar_test(bar(FSmem::bias_full), s & 1);
+      const bool image_free = s < 2 || mbar_test(bar(FSmem::pds_done + buf), ((s >> 1) - 1) & 1);
+      const bool scores_there = mbar_test(bar(FSmem::sd_full), s & 1);
       const float neg_lse2 = -lse_next * kLog2e, neg_delta = -delta_next;
       {
         FWalk ahead = w;
@@ -1244,19 +1245,20 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       }
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
       const uint32_t bits = has_bits ? keep_words[kt * 4 + wg] : 0xffffffffu;
-      // The step's bias words go to registers at once and the staging tile is handed back, so that the next
-      // tile's copy runs under this step's arithmetic.
+      // The step's bias words are requested at once; the staging tile is handed back as soon as they have arrived
+      // (below, after the first scores have been fetched), so that the next tile's copy runs under this step's arithmetic.
       uint4 bias_words[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
       if (HAS_BIAS) {
-        ok = mbar_wait(bar(FSmem::bias_full), s & 1, abort_flag);
+        ok = mbar_wait_probed(bias_there, bar(FSmem::bias_full), s & 1, abort_flag);
         if (!ok) break;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) bias_words[c] = *reinterpret_cast<const uint4*>(swizzled_chunk(bias_row, c));
-        // the loads must have returned before the tile is handed back (the copy of the next tile may land at once)
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          asm volatile("" ::"r"(bias_words[c].x), "r"(bias_words[c].y), "r"(bias_words[c].z), "r"(bias_words[c].w) : "memory");
-        mbar_arrive_warp(bar(FSmem::bias_empty));
+        for (int c = 0; c < 4; ++c) bias_words[c] = lds_v4_here(swizzled_chunk(bias_row, c));
+      }
+      if (s > 0) {
+        // The images of step s - 1 are handed to the products only now: their stores have drained under the work
+        // since, so the fence does not wait, and the accumulating issuer has slack to spare.
+        fence_proxy_async_smem();
+        mbar_arrive_warp(bar(FSmem::pds_full + (buf ^ 1)));
       }
       if (signoff && qi == 0 && warp < 4) {
         // key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory
@@ -1271,8 +1273,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         mbar_arrive_warp(bar(FSmem::k_ready + ks));
       }
       // this step's dS image was last read by the products of step s - 2, the P image by the dV products of s - 1
-      if (s >= 2) ok = mbar_wait(bar(FSmem::pds_done + buf), ((s >> 1) - 1) & 1, abort_flag);
-      if (ok) ok = mbar_wait(bar(FSmem::sd_full), s & 1, abort_flag);
+      ok = mbar_wait_probed(image_free, bar(FSmem::pds_done + buf), ((s >> 1) - 1) & 1, abort_flag);
+      if (ok) ok = mbar_wait_probed(scores_there, bar(FSmem::sd_full), s & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       // image rows are queries; this warpgroup's 32 keys are chunks (wg & 1) * 4 .. + 3 of half (wg >> 1)
@@ -1286,6 +1288,13 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         tmem_ld16(lanes_t + kSCol + wg * 32 + round * 16, sraw);
         tmem_ld16(lanes_t + kDpCol + wg * 32 + round * 16, draw);
         tmem_wait_ld();
+        if (round == 0 && HAS_BIAS) {
+          // the bias words must have returned before the tile is handed back (the copy of the next tile may land at once)
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            asm volatile("" ::"r"(bias_words[c].x), "r"(bias_words[c].y), "r"(bias_words[c].z), "r"(bias_words[c].w) : "memory");
+          mbar_arrive_warp(bar(FSmem::bias_empty));
+        }
         if (round == 1) {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(FSmem::sd_free));
@@ -1317,13 +1326,11 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
             make_uint4(p_packed[4 * c], p_packed[4 * c + 1], p_packed[4 * c + 2], p_packed[4 * c + 3]);
-      fence_proxy_async_smem();
-      mbar_arrive_warp(bar(FSmem::pds_full + buf));
       if (qi == 0 && s > 0) {
         // A new key tile: dK and dV of the previous one are complete once the products of step s - 1 are (a commit
-        // covers every product issued before it); a new group also finds its predecessor's dQ complete.  The images of
-        // step s have been handed over above, so the read-out and its trips to global memory run under this step's
-        // products, which wait for the accumulators through dkv_free / dq_free only.
+        // covers every product issued before it); a new group also finds its predecessor's dQ complete.  The products
+        // of step s, which overwrite these accumulators, are issued after this step's images have been handed over,
+        // which happens at the top of the next step: they wait for the read-out through dkv_free / dq_free only.
         ok = mbar_wait(bar(FSmem::pds_done + ((s - 1) & 1)), ((s - 1) >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
@@ -1331,14 +1338,51 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (kt == 0) store_query_tiles(last_g);
       }
     }
+    const int steps = w.s;
+    if (ok && steps > 0) {  // the images of the last step
+      fence_proxy_async_smem();
+      mbar_arrive_warp(bar(FSmem::pds_full + ((steps - 1) & 1)));
+    }
 
     // every product has finished when the products of the last step have
-    const int steps = w.s;
     if (ok && steps > 0) ok = mbar_wait(bar(FSmem::pds_done + ((steps - 1) & 1)), ((steps - 1) >> 1) & 1, abort_flag);
     if (ok && steps > 0) {
       tc_fence_after_sync();
       store_key_tile(P.groups - 1, KT - 1);
       store_query_tiles(P.groups - 1);
+    }
+    if (P.groups > 1) {
+      // The row's dK and dV now stand complete in this SM's slot (f32, summed group by group in a fixed order by the
+      // thread that owns the key).  Every warp passes the barrier, whatever became of its waits; the 16-bit rows are
+      // then written by all of them: four lanes share a key, so a warp stores eight 64-byte rows per instruction.
+      __threadfence();
+      named_barrier_sync(2, 16 * 32);
+      if (*abort_flag == 0) {
+        const int items = 2 * P.cols * 4;  // (tensor, key, eight channels)
+        for (int item = tid; item < items; item += 16 * 32) {
+          const int j = item & 3, key = (item >> 2) % P.cols, which = (item >> 2) / P.cols;
+          const bool wanted = which == 0 ? P.write_dk != 0 : P.write_dv != 0;
+          if (!wanted) continue;
+          const float4* slot = reinterpret_cast<const float4*>(P.slots) + (int64_t(sm_id) * 2 + which) * 8 * P.slot_keys + key;
+          const float4 lo = ldcg_f4(slot + (2 * j) * P.slot_keys), hi = ldcg_f4(slot + (2 * j + 1) * P.slot_keys);
+          const float f = which == 0 ? scale : 1.f;
+          const oops_ta_pair& o = which == 0 ? P.dk : P.dv;
+          T* dst = reinterpret_cast<T*>(o.ptr) + b * o.sb + int64_t(r) * o.sr + int64_t(key) * o.sc + h * o.sh + j * 8;
+          const uint32_t w0 = Half2<T>::pack(lo.x * f, lo.y * f), w1 = Half2<T>::pack(lo.z * f, lo.w * f);
+          const uint32_t w2 = Half2<T>::pack(hi.x * f, hi.y * f), w3 = Half2<T>::pack(hi.z * f, hi.w * f);
+          if (pair_vec_ok(o)) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
+          } else {
+            unsigned short* d0 = reinterpret_cast<unsigned short*>(dst);
+            const uint32_t ws[4] = {w0, w1, w2, w3};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              d0[2 * i] = (unsigned short)(ws[i] & 0xffffu);
+              d0[2 * i + 1] = (unsigned short)(ws[i] >> 16);
+            }
+          }
+        }
+      }
     }
   }
   teardown(abort_flag, tmem_base, kFScoreWarp);
