@@ -1232,6 +1232,13 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
     int last_g = 0, last_kt = 0;  // group and key tile of the previous step
     for (; !w.done() && ok; last_g = w.g, last_kt = w.kt, w.next()) {
       const int s = w.s, kt = w.kt, qi = w.qi, buf = s & 1;
+      if (s > 0) {
+        // The images of step s - 1 are handed to the products only now: their stores have drained under the read-out
+        // and the loop's turn-around, and the fence stands before anything this step requests, so it does not wait;
+        // the accumulating issuer has slack to spare.
+        fence_proxy_async_smem();
+        mbar_arrive_warp(bar(FSmem::pds_full + (buf ^ 1)));
+      }
       // The three phases the step needs first are probed together (one round trip to the barrier words); in the steady
       // state, where these warps are the slow side of the pipeline, all three are complete.
       const bool bias_there = HAS_BIAS && mbar_test(bar(FSmem::bias_full), s & 1);
@@ -1253,12 +1260,6 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         if (!ok) break;
 #pragma unroll
         for (int c = 0; c < 4; ++c) bias_words[c] = lds_v4_here(swizzled_chunk(bias_row, c));
-      }
-      if (s > 0) {
-        // The images of step s - 1 are handed to the products only now: their stores have drained under the work
-        // since, so the fence does not wait, and the accumulating issuer has slack to spare.
-        fence_proxy_async_smem();
-        mbar_arrive_warp(bar(FSmem::pds_full + (buf ^ 1)));
       }
       if (signoff && qi == 0 && warp < 4) {
         // key rows of dropped keys must not reach the dQ product (0 * inf): clear them in shared memory

@@ -301,7 +301,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         mbar_arrive_warp(bar(FwdSmem::v_ready + st));
       }
 
-      ok = mbar_wait(bar(FwdSmem::s_full + w), j & 1, abort_flag);
+      // the two phases the step needs are probed together: one round trip to the barrier words when both are complete
+      const bool s_there = mbar_test(bar(FwdSmem::s_full + w), j & 1);
+      const bool bias_there = HAS_BIAS && mbar_test(bar(FwdSmem::bias_full + w * 2 + (j & 1)), (j >> 1) & 1);
+      ok = mbar_wait_probed(s_there, bar(FwdSmem::s_full + w), j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       f32x2 x[kKeys / 2];
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
 
       if (HAS_BIAS) {
         const int slot = w * 2 + (j & 1);
-        ok = mbar_wait(bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
+        ok = mbar_wait_probed(bias_there, bar(FwdSmem::bias_full + slot), (j >> 1) & 1, abort_flag);
         if (!ok) break;
         const uint8_t* row = smem_gen + FwdSmem::bias + slot * kBiasBytes + t * 128;
         uint4 bv[8];
