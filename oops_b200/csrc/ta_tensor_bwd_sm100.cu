@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
   uint32_t* keep_words = reinterpret_cast<uint32_t*>(smem_gen + DqSmem::keep);
   auto bar = [&](int index) -> uint32_t { return smem_base + DqSmem::bars + index * 8; };
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
   const int qp = idx % P.q_pairs;
@@ -608,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DkvSmem::tmem_slot);
   auto bar = [&](int index) -> uint32_t { return smem_base + DkvSmem::bars + index * 8; };
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
   const int kp = idx % P.k_pairs;
@@ -979,7 +979,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
   uint32_t* keep_words = reinterpret_cast<uint32_t*>(smem_gen + FSmem::keep);
   auto bar = [&](int index) -> uint32_t { return smem_base + FSmem::bars + index * 8; };
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
   const int h = idx % P.heads;
@@ -1451,7 +1451,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DbSmem::tmem_slot);
   auto bar = [&](int index) -> uint32_t { return smem_base + DbSmem::bars + index * 8; };
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   if (device_failed()) return;
   int idx = blockIdx.x;
   const int kt = idx % P.tiles;

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
   auto bar = [&](int index) -> uint32_t { return smem_base + FwdSmem::bars + index * 8; };
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   if (device_failed()) return;
 
