@@ -199,6 +199,17 @@ int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, i
                           const oops_ta_pair* dgate, void* stream);
 
 /*
+ * Pair validity of a packed ragged batch: for sample s with n_s tokens, out holds the samples' row-major n_s x n_s
+ * squares one after the other, cell (i, j) = token i is valid and token j is valid (bytes 0 / 1).  `token_values` are
+ * bytes (nonzero = valid), `token_offsets` the samples + 1 cumulative token counts (int64, device memory), `chunks`
+ * the sum over samples of n_s * ceil(n_s / 16) (the launch extent, computed by the caller from the lengths it already
+ * has on the host).  Replaces the packed arm of the reference's pair_mask_from_token_mask
+ * (oops/mask/pair_mask_from_token_mask.py:100-103, `packed_pair_mask`); the dense arm is a broadcast AND (:68-70).
+ */
+int oops_ta_pair_mask_packed(const uint8_t* token_values, const int64_t* token_offsets, int32_t samples, int64_t chunks,
+                             uint8_t* out, void* stream);
+
+/*
  * Forward pass that needs no workspace from the caller and allocates nothing.
  *
  * It has no counterpart in the reference.  It is for hosts that cannot hand over scratch memory when

@@ -186,6 +186,19 @@ int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, i
                        dgate ? *dgate : none, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int oops_ta_pair_mask_packed(const uint8_t* token_values, const int64_t* token_offsets, int32_t samples, int64_t chunks,
+                             uint8_t* out, void* stream) {
+  if (samples < 0 || chunks < 0) return fail(OOPS_TA_INVALID_ARGUMENT, "negative sample or chunk count");
+  if (chunks > 0 && (!token_values || !token_offsets || !out))
+    return fail(OOPS_TA_INVALID_ARGUMENT, "token_values, token_offsets or out is NULL");
+  if (samples > packed_pair_mask_max_samples())
+    return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "%d samples in one call (at most %d)", samples, packed_pair_mask_max_samples());
+  const int status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  return packed_pair_mask(token_values, token_offsets, samples, chunks, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int oops_ta_backward(const oops_ta_problem* problem, const oops_ta_pair* out, const oops_ta_pair* dout,
                      const float* lse, const oops_ta_grads* grads, void* stream) {
   int status = validate(problem, true);

@@ -47,6 +47,11 @@ int gate_forward(int dtype, int batch, int rows, int cols, int heads, int head_d
 int gate_backward(int dtype, int batch, int rows, int cols, int heads, int head_dim, const oops_ta_pair& attention,
                   const oops_ta_pair& gate, const oops_ta_pair& dout, const oops_ta_pair& dattention,
                   const oops_ta_pair& dgate, cudaStream_t stream);
+// Pair validity of a packed ragged batch (token bytes, samples + 1 cumulative token counts on the device, number of
+// 16-cell chunks over all rows); at most packed_pair_mask_max_samples() samples per call.
+int packed_pair_mask(const uint8_t* tokens, const int64_t* token_offsets, int samples, int64_t chunks, uint8_t* out,
+                     cudaStream_t stream);
+int packed_pair_mask_max_samples();
 // Forward pass of the tcgen05 kernels with the gate applied in the epilogue: writes sigmoid(gate) * out to `gated`
 // and, when plain.ptr is not NULL, the ungated values to `plain`.
 int tensor_forward_gated(const oops_ta_problem& p, const oops_ta_pair& gate, const oops_ta_pair& gated,

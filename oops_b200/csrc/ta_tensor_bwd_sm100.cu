@@ -1283,40 +1283,41 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       uint8_t* p_row = smem_gen + FSmem::ps + row_at;
       uint8_t* ds_row = smem_gen + FSmem::dss + buf * kFImage + row_at;
       uint32_t p_packed[16];
+      // Eight columns of S and dP at a time; the next eight are requested as soon as the current ones have arrived
+      // and travel under the current eight's arithmetic.
+      uint32_t sraw[2][8], draw[2][8];
+      tmem_ld8(lanes_t + kSCol + wg * 32, sraw[0]);
+      tmem_ld8(lanes_t + kDpCol + wg * 32, draw[0]);
 #pragma unroll
-      for (int round = 0; round < 2; ++round) {
-        uint32_t sraw[16], draw[16];
-        tmem_ld16(lanes_t + kSCol + wg * 32 + round * 16, sraw);
-        tmem_ld16(lanes_t + kDpCol + wg * 32 + round * 16, draw);
+      for (int c8 = 0; c8 < 4; ++c8) {
         tmem_wait_ld();
-        if (round == 0 && HAS_BIAS) {
+        if (c8 == 0 && HAS_BIAS) {
           // the bias words must have returned before the tile is handed back (the copy of the next tile may land at once)
 #pragma unroll
           for (int c = 0; c < 4; ++c)
             asm volatile("" ::"r"(bias_words[c].x), "r"(bias_words[c].y), "r"(bias_words[c].z), "r"(bias_words[c].w) : "memory");
           mbar_arrive_warp(bar(FSmem::bias_empty));
         }
-        if (round == 1) {
+        if (c8 < 3) {
+          tmem_ld8(lanes_t + kSCol + wg * 32 + (c8 + 1) * 8, sraw[(c8 + 1) & 1]);
+          tmem_ld8(lanes_t + kDpCol + wg * 32 + (c8 + 1) * 8, draw[(c8 + 1) & 1]);
+        } else {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(FSmem::sd_free));
         }
+        f32x2 p2[4], ds2[4];
+        score_grad8_words<T, HAS_BIAS>(sraw[c8 & 1], draw[c8 & 1], bias_words[c8], c2, log2e2, nl1, nd1, p2, ds2);
+        if (bits != 0xffffffffu) {
 #pragma unroll
-        for (int i8 = 0; i8 < 2; ++i8) {
-          const int c8 = round * 2 + i8;
-          f32x2 p2[4], ds2[4];
-          score_grad8_words<T, HAS_BIAS>(sraw + i8 * 8, draw + i8 * 8, bias_words[c8], c2, log2e2, nl1, nd1, p2, ds2);
-          if (bits != 0xffffffffu) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              p2[i] = select2(p2[i], bits, c8 * 8 + 2 * i);
-              ds2[i] = select2(ds2[i], bits, c8 * 8 + 2 * i);
-            }
+          for (int i = 0; i < 4; ++i) {
+            p2[i] = select2(p2[i], bits, c8 * 8 + 2 * i);
+            ds2[i] = select2(ds2[i], bits, c8 * 8 + 2 * i);
           }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
-          *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(ds_row, c8))) =
-              make_uint4(pack16<T>(ds2[0]), pack16<T>(ds2[1]), pack16<T>(ds2[2]), pack16<T>(ds2[3]));
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p_packed[c8 * 4 + i] = pack16<T>(p2[i]);
+        *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(ds_row, c8))) =
+            make_uint4(pack16<T>(ds2[0]), pack16<T>(ds2[1]), pack16<T>(ds2[2]), pack16<T>(ds2[3]));
       }
       // the single P image is free once the dV products of the previous step have read it; by now they have
       if (s >= 1) {
