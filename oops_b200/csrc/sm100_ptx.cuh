@@ -357,6 +357,14 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t (&r)[8]) 
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// The registers a tensor-memory load fills are plain asm outputs: nothing ties their readers to the wait above, and
+// the compiler may schedule arithmetic on them before it.  Passing them through an empty volatile statement placed
+// after the wait (volatile statements keep their order) makes every later reader depend on it; it emits no code.
+template <int N>
+__device__ __forceinline__ void tmem_loaded(uint32_t (&r)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i]));
+}
 
 // ---- math ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {

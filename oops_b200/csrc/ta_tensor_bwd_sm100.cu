@@ -498,6 +498,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       tmem_ld32(tile_t + half * 32, sraw);
       tmem_ld32(tile_t + kDpCol + half * 32, draw);
       tmem_wait_ld();
+      tmem_loaded(sraw);
+      tmem_loaded(draw);
       tc_fence_before_sync();
       mbar_arrive_warp(bar(DqSmem::sd_free + w));
       const int slot = w * 2 + (j & 1);
@@ -549,6 +551,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dq_kernel(const _
       uint32_t acc[32];
       tmem_ld32(tile_t + kDqCol, acc);
       tmem_wait_ld();
+      tmem_loaded(acc);
       if (q_valid && P.write_dq) {
         T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
         store_row32<T>(dst, acc, scale, pair_vec_ok(P.dq));
@@ -805,6 +808,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
         tmem_ld16(tile_t + half * 32 + round * 16, sraw);
         tmem_ld16(tile_t + kDpCol + half * 32 + round * 16, draw);
         tmem_wait_ld();
+        tmem_loaded(sraw);
+        tmem_loaded(draw);
         if (round == 1) {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(DkvSmem::sd_free + w));
@@ -854,6 +859,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
       if (half == 0 && P.write_dk) {
         tmem_ld32(tile_t + kDkCol, acc);
         tmem_wait_ld();
+        tmem_loaded(acc);
         if (key < P.cols) {
           T* dst = reinterpret_cast<T*>(P.dk.ptr) + b * P.dk.sb + int64_t(r) * P.dk.sr + int64_t(key) * P.dk.sc + h * P.dk.sh;
           store_row32<T>(dst, acc, scale, pair_vec_ok(P.dk));
@@ -862,6 +868,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) ta_bwd_dkv_kernel(const 
       if (half == 1 && P.write_dv) {
         tmem_ld32(tile_t + kDvCol, acc);
         tmem_wait_ld();
+        tmem_loaded(acc);
         if (key < P.cols) {
           T* dst = reinterpret_cast<T*>(P.dv.ptr) + b * P.dv.sb + int64_t(r) * P.dv.sr + int64_t(key) * P.dv.sc + h * P.dv.sh;
           store_row32<T>(dst, acc, 1.f, pair_vec_ok(P.dv));
@@ -1174,6 +1181,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       uint32_t acc[32];
       tmem_ld32(lanes_t + (wg == 0 ? kDkCol : kDvCol), acc);
       tmem_wait_ld();
+      tmem_loaded(acc);
       tc_fence_before_sync();
       mbar_arrive_warp(bar(FSmem::dkv_free));
       const int key = kt * kTile + t;
@@ -1208,6 +1216,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         uint32_t acc[32];
         tmem_ld32(lanes_t + kDqCol + qi * kHeadDim, acc);
         tmem_wait_ld();
+        tmem_loaded(acc);
         const int q_index = (g * P.tiles_per_group + qi) * kTile + t;
         if (q_index < P.cols && P.write_dq) {
           T* dst = reinterpret_cast<T*>(P.dq.ptr) + b * P.dq.sb + int64_t(r) * P.dq.sr + int64_t(q_index) * P.dq.sc + h * P.dq.sh;
@@ -1291,6 +1300,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
 #pragma unroll
       for (int c8 = 0; c8 < 4; ++c8) {
         tmem_wait_ld();
+        tmem_loaded(sraw[c8 & 1]);
+        tmem_loaded(draw[c8 & 1]);
         if (c8 == 0 && HAS_BIAS) {
           // the bias words must have returned before the tile is handed back (the copy of the next tile may land at once)
 #pragma unroll
@@ -1645,10 +1656,14 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
 #pragma unroll
         for (int quad = 0; quad < 8; quad += 2) {
           tmem_wait_ld();
+          tmem_loaded(s_a);
+          tmem_loaded(d_a);
           tmem_ld4(s_t + (quad + 1) * 4, s_b);
           tmem_ld4(s_t + kTile + (quad + 1) * 4, d_b);
           work4(quad, s_a, d_a);
           tmem_wait_ld();
+          tmem_loaded(s_b);
+          tmem_loaded(d_b);
           if (quad + 2 < 8) {
             tmem_ld4(s_t + (quad + 2) * 4, s_a);
             tmem_ld4(s_t + kTile + (quad + 2) * 4, d_a);

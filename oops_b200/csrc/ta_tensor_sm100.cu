@@ -417,6 +417,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
         uint32_t acc[32];
         tmem_ld32(o_tmem, acc);
         tmem_wait_ld();
+        tmem_loaded(acc);
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
         tmem_st32(o_tmem, acc);
@@ -441,6 +442,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       uint32_t acc[32];
       tmem_ld32(o_tmem, acc);
       tmem_wait_ld();
+      tmem_loaded(acc);
       if (q_index < P.cols) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         uint32_t o2[16];
