@@ -1604,6 +1604,7 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
     uint32_t next_keep;
     load_stats(0, next_lse, next_dl, next_keep);
 
+    bool scores_there = false;  // answer of the probe the previous row sent for this row's scores
     for (int i = 0; i < n_rows && ok; ++i) {
       const int buf = i & 1;
       const float neg_lse2 = -next_lse * kLog2e, neg_delta = -next_dl;
@@ -1612,9 +1613,10 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
       const uint32_t bits = need_bits ? __ballot_sync(0xffffffffu, keep_lane) : 0xffffffffu;
       const f32x2 nl1 = pack2(neg_lse2, neg_lse2), nd1 = pack2(neg_delta, neg_delta);
       const float nl_unit = fmaf(neg_lse2, kUnit, kUnitShift);
-      ok = mbar_wait(bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
+      ok = mbar_wait_probed(scores_there, bar(DbSmem::sd_full + buf), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      scores_there = false;
       const uint32_t s_t = tmem_base + lane_field + buf * 2 * kTile + wg * 32;
       // The row's 32 logits of this thread, four tensor-memory columns of S and of dP at a time.  Rows with a dropped
       // key take a second copy of the body that zeroes the dropped columns: a test per element inside one body
@@ -1655,6 +1657,8 @@ __global__ void __launch_bounds__(kDbThreads, 1) ta_bwd_dbias_kernel(const __gri
         tmem_ld4(s_t + kTile, d_a);
 #pragma unroll
         for (int quad = 0; quad < 8; quad += 2) {
+          // the next row's scores are probed half-way through this row: the answer travels under the arithmetic
+          if (quad == 4 && i + 1 < n_rows) scores_there = mbar_test(bar(DbSmem::sd_full + (buf ^ 1)), ((i + 1) >> 1) & 1);
           tmem_wait_ld();
           tmem_loaded(s_a);
           tmem_loaded(d_a);
