@@ -31,6 +31,26 @@ def _nvcc() -> str:
     return str(candidate) if candidate.exists() else "nvcc"
 
 
+# Kernels that keep tensor-memory loads in flight under arithmetic: a load writes its destination registers when the
+# data arrives, so a spill (or copy) of such a register between issue and wait would save stale data.  ptxas must
+# report no spill stores for them; the build fails otherwise.
+NO_SPILL_KERNELS = ("ta_bwd_fused_kernel", "ta_bwd_dbias_kernel")
+
+
+def _spilling_entries(ptxas_log: str, kernels) -> list:
+    """Entry functions of `kernels` for which `ptxas -v` reports spill stores."""
+    found, current = [], None
+    for line in ptxas_log.splitlines():
+        if "Compiling entry function" in line:
+            current = line.split("'")[1] if "'" in line else line
+        elif "bytes spill stores" in line and current is not None:
+            stores = int(line.split("bytes stack frame,")[1].split("bytes spill stores")[0])
+            if stores > 0 and any(k in current for k in kernels):
+                found.append(f"{current}: {stores} bytes")
+            current = None
+    return found
+
+
 def _stale(target: Path, deps) -> bool:
     if not target.exists():
         return True
@@ -54,6 +74,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             log.write_text(done.stdout + done.stderr)
             if done.returncode != 0:
                 raise RuntimeError(f"nvcc failed for {name}:\n{done.stdout}\n{done.stderr}")
+            spilled = _spilling_entries(done.stdout + done.stderr, NO_SPILL_KERNELS)
+            if spilled:
+                obj.unlink(missing_ok=True)
+                raise RuntimeError(f"{name}: register spills in kernels that keep tensor-memory loads in flight: {spilled}")
             if verbose:
                 print(done.stderr)
         return obj

@@ -308,14 +308,21 @@ __global__ void __launch_bounds__(kFwdThreads, 2) ta_fwd_kernel(const __grid_con
       if (!ok) break;
       tc_fence_after_sync();
       f32x2 x[kKeys / 2];
+      static_assert(kKeys == 64, "two 32-column loads per step");
+      {
+        // nothing stands between the loads and their wait, and the registers are read only after it
+        uint32_t raw0[32], raw1[32];
+        tmem_ld32(s_tmem, raw0);
+        tmem_ld32(s_tmem + 32, raw1);
+        tmem_wait_ld();
+        tmem_loaded(raw0);
+        tmem_loaded(raw1);
 #pragma unroll
-      for (int c = 0; c < kKeys / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(s_tmem + c * 32, raw);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[c * 16 + i] = pack2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
+        for (int i = 0; i < 16; ++i) {
+          x[i] = pack2(__uint_as_float(raw0[2 * i]), __uint_as_float(raw0[2 * i + 1]));
+          x[16 + i] = pack2(__uint_as_float(raw1[2 * i]), __uint_as_float(raw1[2 * i + 1]));
+        }
       }
-      tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive_warp(bar(FwdSmem::s_free + w));
 
