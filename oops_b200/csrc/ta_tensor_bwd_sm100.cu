@@ -1295,6 +1295,7 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
       // Eight columns of S and dP at a time; the next eight are requested as soon as the current ones have arrived
       // and travel under the current eight's arithmetic.
       uint32_t sraw[2][8], draw[2][8];
+      bool p_free = s < 1;
       tmem_ld8(lanes_t + kSCol + wg * 32, sraw[0]);
       tmem_ld8(lanes_t + kDpCol + wg * 32, draw[0]);
 #pragma unroll
@@ -1315,6 +1316,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
         } else {
           tc_fence_before_sync();
           mbar_arrive_warp(bar(FSmem::sd_free));
+          // the P image's phase is probed here; the answer travels under the last eight columns' arithmetic
+          if (s >= 1) p_free = mbar_test(bar(FSmem::p_done), (s - 1) & 1);
         }
         f32x2 p2[4], ds2[4];
         score_grad8_words<T, HAS_BIAS>(sraw[c8 & 1], draw[c8 & 1], bias_words[c8], c2, log2e2, nl1, nd1, p2, ds2);
@@ -1331,10 +1334,8 @@ __global__ void __launch_bounds__(kFThreads, 1) ta_bwd_fused_kernel(const __grid
             make_uint4(pack16<T>(ds2[0]), pack16<T>(ds2[1]), pack16<T>(ds2[2]), pack16<T>(ds2[3]));
       }
       // the single P image is free once the dV products of the previous step have read it; by now they have
-      if (s >= 1) {
-        ok = mbar_wait(bar(FSmem::p_done), (s - 1) & 1, abort_flag);
-        if (!ok) break;
-      }
+      ok = mbar_wait_probed(p_free, bar(FSmem::p_done), (s - 1) & 1, abort_flag);
+      if (!ok) break;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(const_cast<uint8_t*>(swizzled_chunk(p_row, c))) =
