@@ -708,7 +708,41 @@ def main():
             "note": "inference, N=768: sigmoid(gate) * attention in the forward kernel's epilogue against the forward "
                     "kernel followed by the library's element-wise gate kernel",
         }
+        # the layer norm that precedes the projections, on a pair representation of 2048 x 2048 cells (128 channels, bf16,
+        # f32 parameters): HBM-bound byte work, reported against the measured copy bandwidth
+        from oops_b200 import layer_norm
+        hbm_gbs = 6551.4
+        try:
+            hbm_gbs = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"])
+        except Exception:  # noqa: BLE001
+            pass
+        ln_rows, ln_width = 2048 * 2048, 128  # the pair representation of config 5: 1.07 GB per tensor
+        ln_x = torch.randn(ln_rows, ln_width, device=device, dtype=torch.bfloat16).requires_grad_(True)
+        ln_w = torch.ones(ln_width, device=device).requires_grad_(True)
+        ln_b = torch.zeros(ln_width, device=device).requires_grad_(True)
+        ln_up = torch.randn(ln_rows, ln_width, device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            ln_fwd = lambda: layer_norm(ln_x, ln_width, ln_w, ln_b)  # noqa: E731
+            for _ in range(3):
+                ln_fwd()
+            ms_ln_f = timed(ln_fwd, max(args.steps, 10))
+        ln_out = layer_norm(ln_x, ln_width, ln_w, ln_b)
+        ln_bwd = lambda: torch.autograd.grad(ln_out, (ln_x, ln_w, ln_b), ln_up, retain_graph=True)  # noqa: E731
+        for _ in range(3):
+            ln_bwd()
+        ms_ln_b = timed(ln_bwd, max(args.steps, 10))
+        ln_bytes = ln_rows * ln_width * 2
+        ln_entry = {
+            "rows": ln_rows, "width": ln_width, "forward_ms": ms_ln_f, "forward_gbs": 2 * ln_bytes / ms_ln_f / 1e6,
+            "forward_frac_of_hbm": 2 * ln_bytes / ms_ln_f / 1e6 / hbm_gbs, "backward_ms": ms_ln_b,
+            "backward_gbs": 3 * ln_bytes / ms_ln_b / 1e6, "backward_frac_of_hbm": 3 * ln_bytes / ms_ln_b / 1e6 / hbm_gbs,
+            "hbm_peak_gbs": hbm_gbs,
+            "note": "algorithmic bytes: forward reads x and writes y, reverse reads dy and x and writes dx (row statistics "
+                    "and parameter partials are below 2 % of that); inputs larger than L2",
+        }
+        del ln_x, ln_out, ln_up
         line["n768"] = {
+            "layer_norm": ln_entry,
             "workload": WORKLOADS["cfg3"]["label"], "fwd_bwd_ms": ms3, "fwd_bwd_tflops": f3 / ms3 / 1e9,
             "fwd_bwd_frac_of_bf16_peak": f3 / ms3 / 1e9 / peak, "fwd_ms": ms3f, "fwd_tflops": f3f / ms3f / 1e9,
             "fwd_frac_of_bf16_peak": f3f / ms3f / 1e9 / peak, "gated_output": gated_entry,

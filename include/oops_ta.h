@@ -199,6 +199,27 @@ int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, i
                           const oops_ta_pair* dgate, void* stream);
 
 /*
+ * Layer normalisation over the last axis of (rows, width) activations, 1 <= width <= 8192: the step before the
+ * projections that produce q, k, v and the pair bias.  Replaces the backend of the reference's layer_norm
+ * (oops/normalization/layer_norm/layer_norm.py:37-110, `triton_layer_norm`).
+ *   forward:  y = (x - mean) * rstd * weight + bias; `mean` and `rstd` (f32 per row; either may be NULL) are what the
+ *             reverse pass needs.  `weight` / `bias` may be NULL.
+ *   backward: dx, dweight, dbias (each may be NULL) from dy, x, weight, mean, rstd.  The parameter gradients are sums
+ *             over rows: per-CTA f32 partial rows in `workspace` (oops_ta_layer_norm_backward_workspace_bytes) added in
+ *             a fixed order, so the result is bitwise reproducible.
+ * `dtype` is the activation type (OOPS_TA_F32 / F16 / BF16); `affine_dtype` the type of weight, bias and their
+ * gradients: the same, or OOPS_TA_F32 with 16-bit activations.  Rows are contiguous; row strides are in elements.
+ */
+uint64_t oops_ta_layer_norm_backward_workspace_bytes(int64_t rows, int32_t width);
+int oops_ta_layer_norm_forward(int dtype, int affine_dtype, int64_t rows, int32_t width, const void* x, int64_t x_stride,
+                               const void* weight, const void* bias, float eps, void* y, int64_t y_stride, float* mean,
+                               float* rstd, void* stream);
+int oops_ta_layer_norm_backward(int dtype, int affine_dtype, int64_t rows, int32_t width, const void* dy, int64_t dy_stride,
+                                const void* x, int64_t x_stride, const void* weight, const float* mean, const float* rstd,
+                                void* dx, int64_t dx_stride, void* dweight, void* dbias, void* workspace,
+                                uint64_t workspace_bytes, void* stream);
+
+/*
  * Pair validity of a packed ragged batch: for sample s with n_s tokens, out holds the samples' row-major n_s x n_s
  * squares one after the other, cell (i, j) = token i is valid and token j is valid (bytes 0 / 1).  `token_values` are
  * bytes (nonzero = valid), `token_offsets` the samples + 1 cumulative token counts (int64, device memory), `chunks`

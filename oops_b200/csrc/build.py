@@ -18,7 +18,7 @@ CSRC = Path(__file__).resolve().parent
 ROOT = CSRC.parent.parent
 LIB_DIR = CSRC.parent / "lib"
 LIB_PATH = LIB_DIR / "liboops_ta_sm100.so"
-SOURCES = ("ta_api.cu", "ta_generic.cu", "ta_gate.cu", "ta_mask.cu", "ta_tensor_sm100.cu", "ta_tensor_bwd_sm100.cu")
+SOURCES = ("ta_api.cu", "ta_generic.cu", "ta_gate.cu", "ta_mask.cu", "ta_layer_norm.cu", "ta_tensor_sm100.cu", "ta_tensor_bwd_sm100.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",

@@ -186,6 +186,51 @@ int oops_ta_gate_backward(int dtype, int batch, int rows, int cols, int heads, i
                        dgate ? *dgate : none, reinterpret_cast<cudaStream_t>(stream));
 }
 
+uint64_t oops_ta_layer_norm_backward_workspace_bytes(int64_t rows, int32_t width) {
+  return layer_norm_backward_workspace_bytes(rows, width);
+}
+
+static int check_layer_norm(int64_t rows, int32_t width, int64_t a_stride, int64_t b_stride) {
+  if (rows < 0) return fail(OOPS_TA_INVALID_ARGUMENT, "negative row count");
+  if (width < 1 || width > layer_norm_max_width())
+    return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "layer_norm width %d outside [1, %d]", width, layer_norm_max_width());
+  if (rows > 1 && (a_stride < width || b_stride < width))
+    return fail(OOPS_TA_UNSUPPORTED_LAYOUT, "layer_norm rows overlap (row stride below the width)");
+  return OOPS_TA_OK;
+}
+
+int oops_ta_layer_norm_forward(int dtype, int affine_dtype, int64_t rows, int32_t width, const void* x, int64_t x_stride,
+                               const void* weight, const void* bias, float eps, void* y, int64_t y_stride, float* mean,
+                               float* rstd, void* stream) {
+  int status = check_layer_norm(rows, width, x_stride, y_stride);
+  if (status) return status;
+  if (rows > 0 && (!x || !y)) return fail(OOPS_TA_INVALID_ARGUMENT, "x or y is NULL");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  status = layer_norm_forward(dtype, affine_dtype, rows, width, x, x_stride, weight, bias, eps, y, y_stride, mean, rstd,
+                              reinterpret_cast<cudaStream_t>(stream));
+  return status == OOPS_TA_UNSUPPORTED_DTYPE ? fail(status, "layer_norm dtype %d / parameter dtype %d", dtype, affine_dtype) : status;
+}
+
+int oops_ta_layer_norm_backward(int dtype, int affine_dtype, int64_t rows, int32_t width, const void* dy, int64_t dy_stride,
+                                const void* x, int64_t x_stride, const void* weight, const float* mean, const float* rstd,
+                                void* dx, int64_t dx_stride, void* dweight, void* dbias, void* workspace,
+                                uint64_t workspace_bytes, void* stream) {
+  int status = check_layer_norm(rows, width, x_stride, dy_stride);
+  if (status) return status;
+  if (rows > 0 && (!x || !dy || !mean || !rstd)) return fail(OOPS_TA_INVALID_ARGUMENT, "dy, x, mean or rstd is NULL");
+  if (rows > 0 && (dweight || dbias) &&
+      (!workspace || workspace_bytes < layer_norm_backward_workspace_bytes(rows, width)))
+    return fail(OOPS_TA_INVALID_ARGUMENT, "layer_norm workspace too small for the parameter gradients");
+  status = check_device();
+  if (status) return status;
+  g_error[0] = 0;
+  status = layer_norm_backward(dtype, affine_dtype, rows, width, dy, dy_stride, x, x_stride, weight, mean, rstd, dx, dx_stride,
+                               dweight, dbias, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return status == OOPS_TA_UNSUPPORTED_DTYPE ? fail(status, "layer_norm dtype %d / parameter dtype %d", dtype, affine_dtype) : status;
+}
+
 int oops_ta_pair_mask_packed(const uint8_t* token_values, const int64_t* token_offsets, int32_t samples, int64_t chunks,
                              uint8_t* out, void* stream) {
   if (samples < 0 || chunks < 0) return fail(OOPS_TA_INVALID_ARGUMENT, "negative sample or chunk count");

@@ -52,6 +52,15 @@ int gate_backward(int dtype, int batch, int rows, int cols, int heads, int head_
 int packed_pair_mask(const uint8_t* tokens, const int64_t* token_offsets, int samples, int64_t chunks, uint8_t* out,
                      cudaStream_t stream);
 int packed_pair_mask_max_samples();
+// Layer normalisation over the last axis of (rows, width) activations (row strides in elements, contiguous rows);
+// weight / bias / gradients of them may be NULL; affine_dtype is the activation dtype or f32.
+uint64_t layer_norm_backward_workspace_bytes(int64_t rows, int width);
+int layer_norm_max_width();
+int layer_norm_forward(int dtype, int affine_dtype, int64_t rows, int width, const void* x, int64_t x_stride, const void* weight,
+                       const void* bias, float eps, void* y, int64_t y_stride, float* mean, float* rstd, cudaStream_t stream);
+int layer_norm_backward(int dtype, int affine_dtype, int64_t rows, int width, const void* dy, int64_t dy_stride, const void* x,
+                        int64_t x_stride, const void* weight, const float* mean, const float* rstd, void* dx, int64_t dx_stride,
+                        void* dweight, void* dbias, void* workspace, cudaStream_t stream);
 // Forward pass of the tcgen05 kernels with the gate applied in the epilogue: writes sigmoid(gate) * out to `gated`
 // and, when plain.ptr is not NULL, the ungated values to `plain`.
 int tensor_forward_gated(const oops_ta_problem& p, const oops_ta_pair& gate, const oops_ta_pair& gated,

@@ -36,7 +36,8 @@ EXPORTS = (
     "oops_ta_uses_tensor_path", "oops_ta_forward_workspace_bytes", "oops_ta_backward_workspace_bytes",
     "oops_ta_forward", "oops_ta_backward", "oops_ta_launch_count", "oops_ta_device_status",
     "oops_ta_forward_static", "oops_ta_forward_static_capacity", "oops_ta_selftest_wait_limit",
-    "oops_ta_forward_gated", "oops_ta_gate_forward", "oops_ta_gate_backward", "oops_ta_pair_mask_packed",
+    "oops_ta_forward_gated", "oops_ta_gate_forward", "oops_ta_gate_backward", "oops_ta_pair_mask_packed", "oops_ta_layer_norm_backward_workspace_bytes", "oops_ta_layer_norm_forward",
+    "oops_ta_layer_norm_backward",
 )
 
 
@@ -110,6 +111,15 @@ def library() -> ctypes.CDLL:
     lib.oops_ta_gate_backward.argtypes = [c_int] * 6 + [POINTER(Pair)] * 5 + [c_void_p]
     lib.oops_ta_pair_mask_packed.restype = c_int
     lib.oops_ta_pair_mask_packed.argtypes = [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p]
+    lib.oops_ta_layer_norm_backward_workspace_bytes.restype = c_uint64
+    lib.oops_ta_layer_norm_backward_workspace_bytes.argtypes = [c_int64, c_int32]
+    lib.oops_ta_layer_norm_forward.restype = c_int
+    lib.oops_ta_layer_norm_forward.argtypes = [c_int, c_int, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_void_p, c_float,
+                                               c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+    lib.oops_ta_layer_norm_backward.restype = c_int
+    lib.oops_ta_layer_norm_backward.argtypes = [c_int, c_int, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                                c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_uint64,
+                                                c_void_p]
     lib.oops_ta_selftest_wait_limit.restype = c_int
     lib.oops_ta_selftest_wait_limit.argtypes = [c_void_p]
     lib.oops_ta_device_status.restype = c_int
