@@ -21,7 +21,13 @@ namespace {
 constexpr int kLnWarps = 8;             // warps (= rows in flight) per CTA
 constexpr int kLnCached = 1024;         // widest row kept in registers
 constexpr int kLnPerLane = kLnCached / 32;
-constexpr int kLnCtasPerSm = 4;        // resident CTAs the row-sharing kernels are compiled for (register cap 64)
+#ifndef TA_LN_CTAS
+#define TA_LN_CTAS 4
+#endif
+#ifndef TA_LN_UNROLL
+#define TA_LN_UNROLL 4
+#endif
+constexpr int kLnCtasPerSm = TA_LN_CTAS;        // resident CTAs the row-sharing kernels are compiled for (register cap 64)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -264,7 +270,7 @@ __global__ void __launch_bounds__(kLnWarps * 32) layer_norm_backward_kernel(LnSh
 // ---- rows of up to 1024 elements with 16-byte accesses: LPR lanes share a row, each holding GROUPS groups of V
 // elements; a warp works on 32 / LPR rows at once and on kLnUnroll such row blocks per loop turn, so that enough
 // loads are in flight to cover the memory latency (a 128-channel bf16 row is only 256 bytes).
-constexpr int kLnUnroll = 4;
+constexpr int kLnUnroll = TA_LN_UNROLL;
 
 template <int LPR>
 __device__ __forceinline__ float row_sum(float v) {
