@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 
 #include <initializer_list>
+#include <type_traits>
 
 #include "ta_internal.h"
 
@@ -65,16 +66,6 @@ struct LnVec {
     }
   }
 };
-
-// 16 bytes of a row kept as loaded (four registers) and widened to f32 only where the arithmetic needs them: the
-// kernels below keep several rows in flight per lane, and f32 copies of 16-bit data would double their registers.
-template <typename T, int V>
-__device__ __forceinline__ void ln_unpack(const uint4& raw, float (&out)[V]) {
-  static_assert(V * sizeof(T) == 16, "a raw group is 16 bytes");
-  const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < V; ++i) out[i] = float(e[i]);
-}
 
 // First element of group g of lane `lane`: a warp's accesses are 32 * V contiguous elements.
 template <int V>
@@ -279,24 +270,72 @@ __device__ __forceinline__ float row_sum(float v) {
   return v;
 }
 
+// Packed arithmetic: a group of V elements is V / 2 pairs of f32, and every add / multiply-add below works on a pair
+// (fma.rn.f32x2 and friends), which halves the instructions per byte; 16-bit rows were bound by instruction issue.
+typedef float2 ln2;
+__device__ __forceinline__ ln2 ln_fma2(ln2 a, ln2 b, ln2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ ln2 ln_add2(ln2 a, ln2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ ln2 ln_mul2(ln2 a, ln2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ ln2 ln_both(float v) { return make_float2(v, v); }
+
+template <typename T, int V>
+__device__ __forceinline__ void ln_unpack2(const uint4& raw, ln2 (&out)[V / 2]) {
+  static_assert(V * sizeof(T) == 16, "a raw group is 16 bytes");
+  if constexpr (sizeof(T) == 4) {
+    out[0] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+    out[1] = make_float2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+  } else {
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        out[i] = make_float2(__uint_as_float(words[i] << 16), __uint_as_float(words[i] & 0xffff0000u));
+      } else {
+        out[i] = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+      }
+    }
+  }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ uint4 ln_pack2(const ln2 (&in)[V / 2]) {
+  if constexpr (sizeof(T) == 4) {
+    return make_uint4(__float_as_uint(in[0].x), __float_as_uint(in[0].y), __float_as_uint(in[1].x), __float_as_uint(in[1].y));
+  } else {
+    uint32_t words[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const __nv_bfloat162 h = __float22bfloat162_rn(in[i]);
+        words[i] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __float22half2_rn(in[i]);
+        words[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    return make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
 template <typename T, typename A, int V, int GROUPS, int LPR>
 __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1) layer_norm_forward_rows_kernel(LnShape s, const T* __restrict__ x,
                                                                                 const void* __restrict__ weight,
                                                                                 const void* __restrict__ bias, float eps,
                                                                                 T* __restrict__ y, float* __restrict__ mean_out,
                                                                                 float* __restrict__ rstd_out) {
-  constexpr int kRowsPerWarp = 32 / LPR;
+  constexpr int kRowsPerWarp = 32 / LPR, P = V / 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
   const float inv_width = 1.f / float(s.width);
-  // this lane's affine parameters, fetched once
-  float w[GROUPS][V], b[GROUPS][V];
+  // this lane's affine parameters, fetched once (zero outside the row)
+  ln2 w[GROUPS][P], b[GROUPS][P];
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g)
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const int i = (g * LPR + l) * V + e;
-      w[g][e] = i < s.width ? affine_at<A>(weight, i, 1.f) : 0.f;
-      b[g][e] = i < s.width ? affine_at<A>(bias, i, 0.f) : 0.f;
+    for (int e = 0; e < P; ++e) {
+      const int i = (g * LPR + l) * V + 2 * e;
+      const bool in = i < s.width;
+      w[g][e] = make_float2(in ? affine_at<A>(weight, i, 1.f) : 0.f, in ? affine_at<A>(weight, i + 1, 1.f) : 0.f);
+      b[g][e] = make_float2(in ? affine_at<A>(bias, i, 0.f) : 0.f, in ? affine_at<A>(bias, i + 1, 0.f) : 0.f);
     }
   const int64_t blocks = (s.rows + kRowsPerWarp - 1) / kRowsPerWarp;  // row blocks of one warp
   const int64_t stride = int64_t(gridDim.x) * kLnWarps;
@@ -317,42 +356,41 @@ __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1)
     for (int u = 0; u < kLnUnroll; ++u) {
       const int64_t row = (blk0 + u * stride) * kRowsPerWarp + sub;
       const bool live = blk0 + u * stride < blocks && row < s.rows;
-      float sum = 0.f;
+      ln2 v[GROUPS][P];
+      ln2 sum2 = ln_both(0.f);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
-        float v[V];
-        ln_unpack<T, V>(raw[u][g], v);
+        ln_unpack2<T, V>(raw[u][g], v[g]);
 #pragma unroll
-        for (int e = 0; e < V; ++e) sum += v[e];
+        for (int e = 0; e < P; ++e) sum2 = ln_add2(sum2, v[g][e]);
       }
-      const float mean = row_sum<LPR>(sum) * inv_width;
-      float sq = 0.f;
+      const float mean = row_sum<LPR>(sum2.x + sum2.y) * inv_width;
+      const ln2 neg_mean = ln_both(-mean);
+      ln2 sq2 = ln_both(0.f);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g)
         if ((g * LPR + l) * V < s.width) {
-          float v[V];
-          ln_unpack<T, V>(raw[u][g], v);
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            const float d = v[e] - mean;
-            sq += d * d;
+          for (int e = 0; e < P; ++e) {
+            v[g][e] = ln_add2(v[g][e], neg_mean);  // centred from here on
+            sq2 = ln_fma2(v[g][e], v[g][e], sq2);
           }
         }
-      const float rstd = rsqrtf(row_sum<LPR>(sq) * inv_width + eps);
+      const float rstd = rsqrtf(row_sum<LPR>(sq2.x + sq2.y) * inv_width + eps);
       if (!live) continue;
       if (l == 0) {
         if (mean_out) mean_out[row] = mean;
         if (rstd_out) rstd_out[row] = rstd;
       }
+      const ln2 rstd2 = ln_both(rstd);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
         const int i = (g * LPR + l) * V;
         if (i < s.width) {
-          float v[V], out[V];
-          ln_unpack<T, V>(raw[u][g], v);
+          ln2 out[P];
 #pragma unroll
-          for (int e = 0; e < V; ++e) out[e] = (v[e] - mean) * rstd * w[g][e] + b[g][e];
-          LnVec<T, V>::store(y + row * s.y_stride + i, out);
+          for (int e = 0; e < P; ++e) out[e] = ln_fma2(ln_mul2(v[g][e], rstd2), w[g][e], b[g][e]);
+          *reinterpret_cast<uint4*>(y + row * s.y_stride + i) = ln_pack2<T, V>(out);
         }
       }
     }
@@ -367,24 +405,25 @@ __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1)
                                                                                  const float* __restrict__ rstd_in,
                                                                                  T* __restrict__ dx, float* __restrict__ dw_parts,
                                                                                  float* __restrict__ db_parts) {
-  constexpr int kRowsPerWarp = 32 / LPR;
+  constexpr int kRowsPerWarp = 32 / LPR, P = V / 2;
   constexpr int kU = kLnUnroll / 2;  // two tensors are read per row
   extern __shared__ float ln_smem[];  // [kLnWarps * kRowsPerWarp][width] when partials are wanted
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
   const float inv_width = 1.f / float(s.width);
-  float w[GROUPS][V], dw[GROUPS][V], db[GROUPS][V];
+  ln2 w[GROUPS][P], dw[GROUPS][P], db[GROUPS][P];
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g)
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const int i = (g * LPR + l) * V + e;
-      w[g][e] = i < s.width ? affine_at<A>(weight, i, 1.f) : 0.f;
-      dw[g][e] = db[g][e] = 0.f;
+    for (int e = 0; e < P; ++e) {
+      const int i = (g * LPR + l) * V + 2 * e;
+      const bool in = i < s.width;
+      w[g][e] = make_float2(in ? affine_at<A>(weight, i, 1.f) : 0.f, in ? affine_at<A>(weight, i + 1, 1.f) : 0.f);
+      dw[g][e] = db[g][e] = ln_both(0.f);
     }
   const int64_t blocks = (s.rows + kRowsPerWarp - 1) / kRowsPerWarp;
   const int64_t stride = int64_t(gridDim.x) * kLnWarps;
   for (int64_t blk0 = int64_t(blockIdx.x) * kLnWarps + warp; blk0 < blocks; blk0 += stride * kU) {
-    float xv[kU][GROUPS][V], gv[kU][GROUPS][V];
+    uint4 xraw[kU][GROUPS], graw[kU][GROUPS];
     float mean[kU], rstd[kU];
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
@@ -395,11 +434,10 @@ __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1)
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
         const int i = (g * LPR + l) * V;
-#pragma unroll
-        for (int e = 0; e < V; ++e) xv[u][g][e] = gv[u][g][e] = 0.f;
+        xraw[u][g] = graw[u][g] = make_uint4(0, 0, 0, 0);
         if (live && i < s.width) {
-          LnVec<T, V>::load(x + row * s.x_stride + i, xv[u][g]);
-          LnVec<T, V>::load(dy + row * s.dy_stride + i, gv[u][g]);
+          xraw[u][g] = *reinterpret_cast<const uint4*>(x + row * s.x_stride + i);
+          graw[u][g] = *reinterpret_cast<const uint4*>(dy + row * s.dy_stride + i);
         }
       }
     }
@@ -407,33 +445,36 @@ __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1)
     for (int u = 0; u < kU; ++u) {
       const int64_t row = (blk0 + u * stride) * kRowsPerWarp + sub;
       const bool live = blk0 + u * stride < blocks && row < s.rows;
-      float c1 = 0.f, c2 = 0.f;
+      const ln2 rstd2 = ln_both(rstd[u]), neg_mean2 = ln_both(-mean[u]);
+      ln2 xh[GROUPS][P], gw[GROUPS][P];
+      ln2 c1 = ln_both(0.f), c2 = ln_both(0.f);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
+        ln2 gv[P];
+        ln_unpack2<T, V>(xraw[u][g], xh[g]);
+        ln_unpack2<T, V>(graw[u][g], gv);
         const bool inside = live && (g * LPR + l) * V < s.width;
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const float xhat = inside ? (xv[u][g][e] - mean[u]) * rstd[u] : 0.f;
-          dw[g][e] += gv[u][g][e] * xhat;
-          db[g][e] += gv[u][g][e];
-          const float gw = gv[u][g][e] * w[g][e];
-          xv[u][g][e] = xhat;
-          gv[u][g][e] = gw;
-          c1 += gw * xhat;
-          c2 += gw;
+        for (int e = 0; e < P; ++e) {
+          xh[g][e] = inside ? ln_mul2(ln_add2(xh[g][e], neg_mean2), rstd2) : ln_both(0.f);
+          dw[g][e] = ln_fma2(gv[e], xh[g][e], dw[g][e]);
+          db[g][e] = ln_add2(db[g][e], gv[e]);
+          gw[g][e] = ln_mul2(gv[e], w[g][e]);
+          c1 = ln_fma2(gw[g][e], xh[g][e], c1);
+          c2 = ln_add2(c2, gw[g][e]);
         }
       }
-      c1 = row_sum<LPR>(c1) * inv_width;
-      c2 = row_sum<LPR>(c2) * inv_width;
+      const float m1 = row_sum<LPR>(c1.x + c1.y) * inv_width, m2 = row_sum<LPR>(c2.x + c2.y) * inv_width;
       if (!live || !dx) continue;
+      const ln2 neg_m1 = ln_both(-m1), neg_m2 = ln_both(-m2);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
         const int i = (g * LPR + l) * V;
         if (i < s.width) {
-          float out[V];
+          ln2 out[P];
 #pragma unroll
-          for (int e = 0; e < V; ++e) out[e] = rstd[u] * (gv[u][g][e] - c2 - xv[u][g][e] * c1);
-          LnVec<T, V>::store(dx + row * s.dx_stride + i, out);
+          for (int e = 0; e < P; ++e) out[e] = ln_mul2(ln_fma2(xh[g][e], neg_m1, ln_add2(gw[g][e], neg_m2)), rstd2);
+          *reinterpret_cast<uint4*>(dx + row * s.dx_stride + i) = ln_pack2<T, V>(out);
         }
       }
     }
@@ -447,9 +488,13 @@ __global__ void __launch_bounds__(kLnWarps * 32, GROUPS == 1 ? kLnCtasPerSm : 1)
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g)
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const int i = (g * LPR + l) * V + e;
-          if (i < s.width) ln_smem[(warp * kRowsPerWarp + sub) * s.width + i] = pass == 0 ? dw[g][e] : db[g][e];
+        for (int e = 0; e < P; ++e) {
+          const int i = (g * LPR + l) * V + 2 * e;
+          if (i < s.width) {
+            const ln2 v = pass == 0 ? dw[g][e] : db[g][e];
+            ln_smem[(warp * kRowsPerWarp + sub) * s.width + i] = v.x;
+            ln_smem[(warp * kRowsPerWarp + sub) * s.width + i + 1] = v.y;
+          }
         }
       __syncthreads();
       for (int i = threadIdx.x; i < s.width; i += kLnWarps * 32) {
