@@ -11,8 +11,9 @@ from oops_b200 import (  # noqa: F401
     OOpsUnsupportedError,
     gate_attention_output,
     layer_norm,
+    pair_bias_attention,
     pair_mask_from_token_mask,
     triangle_attention,
 )
 
-__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "pair_mask_from_token_mask", "layer_norm"]
+__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "pair_mask_from_token_mask", "layer_norm", "pair_bias_attention"]
