@@ -14,6 +14,7 @@ from oops_b200 import (  # noqa: F401
     pair_bias_attention,
     pair_mask_from_token_mask,
     triangle_attention,
+    triangle_multiplication,
 )
 
-__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "pair_mask_from_token_mask", "layer_norm", "pair_bias_attention"]
+__all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "pair_mask_from_token_mask", "layer_norm", "pair_bias_attention", "triangle_multiplication"]

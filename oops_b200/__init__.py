@@ -11,7 +11,9 @@ from ._errors import OOpsUnsupportedError
 from .attention import gate_attention_output, pair_bias_attention, triangle_attention, triangle_attention_gated
 from .mask import pair_mask_from_token_mask
 from .normalization import layer_norm
+from .pair import triangle_multiplication
 from .runtime.nested_tensor import NestedTensor
 
 __all__ = ["OOpsUnsupportedError", "NestedTensor", "triangle_attention", "gate_attention_output", "triangle_attention_gated",
-           "pair_mask_from_token_mask", "layer_norm", "pair_bias_attention"]
+           "pair_mask_from_token_mask", "layer_norm", "pair_bias_attention",
+           "triangle_multiplication"]
