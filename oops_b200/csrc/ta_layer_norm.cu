@@ -524,14 +524,29 @@ __global__ void layer_norm_wide_parts_kernel(LnShape s, const T* __restrict__ dy
   if (db_parts) db_parts[int64_t(blockIdx.y) * s.width + col] = db;
 }
 
-// out[col] = sum over parts (in part order) of parts[part][col], stored in the parameter's type.
+// out[col] = sum over parts of parts[part][col], stored in the parameter's type, for dweight (blockIdx.y = 0) and
+// dbias (1) in one launch.  A block owns 32 columns; its eight warps each add every eighth partial row (coalesced
+// 128-byte reads), and the eight sums are added in warp order: the order is fixed, so the result is reproducible.
 template <typename A>
-__global__ void layer_norm_reduce_parts_kernel(const float* __restrict__ parts, int num_parts, int width, A* __restrict__ out) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= width) return;
+__global__ void __launch_bounds__(256) layer_norm_reduce_parts_kernel(const float* __restrict__ dw_parts,
+                                                                      const float* __restrict__ db_parts, int num_parts, int width,
+                                                                      A* __restrict__ dweight, A* __restrict__ dbias) {
+  __shared__ float sums[8][32];
+  const float* parts = blockIdx.y == 0 ? dw_parts : db_parts;
+  A* out = blockIdx.y == 0 ? dweight : dbias;
+  if (!parts || !out) return;  // the whole block takes the same branch
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, col = blockIdx.x * 32 + lane;
   float total = 0.f;
-  for (int p = 0; p < num_parts; ++p) total += parts[int64_t(p) * width + col];
-  out[col] = A(total);
+  if (col < width)
+    for (int p = warp; p < num_parts; p += 8) total += parts[int64_t(p) * width + col];
+  sums[warp][lane] = total;
+  __syncthreads();
+  if (warp == 0 && col < width) {
+    float all = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) all += sums[w][lane];
+    out[col] = A(all);
+  }
 }
 
 constexpr int kLnMaxWidth = 8192;
@@ -628,10 +643,9 @@ int backward_typed(const LnShape& s, const void* dy, const void* x, const void* 
                                                                                                   dw_parts, db_parts);
       count_launch();
     }
-    const int blocks = (s.width + 127) / 128;
-    if (dweight) layer_norm_reduce_parts_kernel<A><<<blocks, 128, 0, stream>>>(dw_parts, num_parts, s.width, reinterpret_cast<A*>(dweight));
-    if (dbias) layer_norm_reduce_parts_kernel<A><<<blocks, 128, 0, stream>>>(db_parts, num_parts, s.width, reinterpret_cast<A*>(dbias));
-    count_launch(int(dweight != nullptr) + int(dbias != nullptr));
+    layer_norm_reduce_parts_kernel<A><<<dim3((s.width + 31) / 32, 2), 256, 0, stream>>>(
+        dw_parts, db_parts, num_parts, s.width, reinterpret_cast<A*>(dweight), reinterpret_cast<A*>(dbias));
+    count_launch();
   }
   return cudaGetLastError() == cudaSuccess ? OOPS_TA_OK : OOPS_TA_CUDA_ERROR;
 }
