@@ -26,26 +26,38 @@ def _square_elements(token_mask, values: Tensor, lengths):
     return type(token_mask)._from_parts(values, [(n, n) for n in lengths], (0, 1), (0, 1))
 
 
+def _dense(token_mask: Tensor) -> Tensor:
+    if token_mask.dim() == 0:
+        raise ValueError(f"{_NAME} token_mask must have at least one dimension")
+    valid = token_mask.bool()
+    return valid.unsqueeze(-1) & valid.unsqueeze(-2)
+
+
+def _packed_tokens(batch) -> Tensor:
+    """The packed token bytes of a ragged batch of (N_i,) elements, after the checks the kernel relies on."""
+    canonical = batch.batch_first and batch.dim() == 2 and tuple(batch.ragged_dims) == (0,) and tuple(batch.packed_dim_order) == (0,)
+    if not canonical:
+        raise ValueError(f"{_NAME} nested elements require canonical (N_i,) packing")
+    if len(batch) == 0:
+        raise unsupported(_NAME, "does not serve an empty NestedTensor wrapper batch without retained element rank")
+    values = batch.concat
+    refusals = (
+        (values.is_complex(), "requires bool, integer, or floating-point packed values", {"dtype": values.dtype}),
+        (values.dim() != 1 or not values.is_contiguous(), "requires contiguous one-dimensional packed token values",
+         {"packed_shape": tuple(values.shape)}),
+        (not values.is_cuda, "requires CUDA packed values", {"device": values.device}),
+    )
+    for refused, reason, context in refusals:
+        if refused:
+            raise unsupported(_NAME, reason, **context)
+    return values.bool()
+
+
 def pair_mask_from_token_mask(token_mask):
     """Outer conjunction of token validity; see the module docstring.  Nonzero values count as valid."""
     if not is_nested(token_mask):
-        if token_mask.dim() < 1:
-            raise ValueError(f"{_NAME} token_mask must have at least one dimension")
-        dense = token_mask.bool()
-        return dense[..., :, None] & dense[..., None, :]
-    if (not token_mask.batch_first or token_mask.dim() != 2 or tuple(token_mask.ragged_dims) != (0,)
-            or tuple(token_mask.packed_dim_order) != (0,)):
-        raise ValueError(f"{_NAME} nested elements require canonical (N_i,) packing")
-    if len(token_mask) == 0:
-        raise unsupported(_NAME, "does not serve an empty NestedTensor wrapper batch without retained element rank")
-    packed = token_mask.concat
-    if packed.is_complex():
-        raise unsupported(_NAME, "requires bool, integer, or floating-point packed values", dtype=packed.dtype)
-    tokens = packed.bool()
-    if tokens.dim() != 1 or not tokens.is_contiguous():
-        raise unsupported(_NAME, "requires contiguous one-dimensional packed token values", packed_shape=tuple(tokens.shape))
-    if not tokens.is_cuda:
-        raise unsupported(_NAME, "requires CUDA packed values", device=tokens.device)
+        return _dense(token_mask)
+    tokens = _packed_tokens(token_mask)
 
     if hasattr(token_mask, "host_offsets"):
         bounds = token_mask.host_offsets(0)

@@ -1,7 +1,5 @@
-"""pair_mask_from_token_mask: dense results and argument contract (no GPU).
-
-Cases follow the reference's tests/mask/test_pair_mask_from_token_mask.py (:30-33 reference formula, :47-52 dense
-dtypes, :73-88 contract)."""
+"""pair_mask_from_token_mask without a GPU: dense results for several dtypes and ranks, and the argument contract
+(what the reference's tests/mask/test_pair_mask_from_token_mask.py checks on the dense arm and for refusals)."""
 
 import pytest
 import torch
@@ -9,33 +7,33 @@ import torch
 import oops_b200 as oops
 
 
-def _reference(mask):
-    token = mask.bool()
-    return token[..., :, None] & token[..., None, :]
+def _outer_and(tokens):
+    valid = tokens != 0
+    return valid.unsqueeze(-1) & valid.unsqueeze(-2)
 
 
-@pytest.mark.parametrize("dtype", [torch.bool, torch.int64, torch.float32])
-def test_dense(dtype):
-    mask = torch.tensor([[1, 0, 2], [0, -1, 3]], dtype=dtype)
-    actual = oops.pair_mask_from_token_mask(mask)
-    assert actual.dtype is torch.bool
-    torch.testing.assert_close(actual, _reference(mask), atol=0, rtol=0)
+@pytest.mark.parametrize("dtype", [torch.bool, torch.int64, torch.float32, torch.uint8])
+@pytest.mark.parametrize("shape", [(5,), (2, 3), (2, 1, 7)])
+def test_dense_matches_the_outer_conjunction(dtype, shape):
+    gen = torch.Generator().manual_seed(11)
+    tokens = (torch.randint(-2, 3, shape, generator=gen)).to(dtype) if dtype is not torch.bool else torch.rand(shape, generator=gen) > 0.4
+    got = oops.pair_mask_from_token_mask(tokens)
+    assert got.dtype is torch.bool and got.shape == (*shape, shape[-1])
+    assert torch.equal(got, _outer_and(tokens))
 
 
-def test_dense_feeds_triangle_attention_shape():
-    tok = torch.arange(12) < 9
-    assert oops.pair_mask_from_token_mask(tok[None]).shape == (1, 12, 12)
+def test_dense_result_is_a_triangle_attention_mask():
+    tokens = torch.arange(12) < 9
+    assert oops.pair_mask_from_token_mask(tokens[None]).shape == (1, 12, 12)
 
 
-@pytest.mark.parametrize("case", ["rank", "cpu_nested", "complex", "nested_rank"])
-def test_contract(case):
-    if case == "rank":
-        with pytest.raises(ValueError):
-            oops.pair_mask_from_token_mask(torch.tensor(True))
-        return
-    shape = (2, 1) if case == "nested_rank" else (2,)
-    dtype = torch.complex64 if case == "complex" else torch.bool
-    mask = oops.NestedTensor([torch.ones(shape, dtype=dtype)], ragged_dims=(0,))
-    error = ValueError if case == "nested_rank" else oops.OOpsUnsupportedError
+def test_scalar_is_refused():
+    with pytest.raises(ValueError):
+        oops.pair_mask_from_token_mask(torch.tensor(True))
+
+
+@pytest.mark.parametrize("kind,error", [("cpu", oops.OOpsUnsupportedError), ("complex", oops.OOpsUnsupportedError), ("rank", ValueError)])
+def test_packed_batches_are_refused_when_unservable(kind, error):
+    element = torch.ones((2, 1) if kind == "rank" else (2,), dtype=torch.complex64 if kind == "complex" else torch.bool)
     with pytest.raises(error):
-        oops.pair_mask_from_token_mask(mask)
+        oops.pair_mask_from_token_mask(oops.NestedTensor([element], ragged_dims=(0,)))
